@@ -11,5 +11,5 @@ timeout 600 python bench.py --impl reference --steps 20 --warmup 5 > gpurun_out/
 B="python bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-gpu-reference --no-parity"
 # whole-token kernel launches: 4086 hydrate, then e2e 3 + 2 (logits mode, pos 4086..4090), then device loop 3 + 2 (greedy mode)
 timeout 900 ncu --metrics gpu__time_duration.sum --clock-control none -k regex:decode_mega --launch-skip 4080 --launch-count 16 --csv --log-file gpurun_out/launches_r2a.csv $B > gpurun_out/ncu_launches.log 2>&1; echo "ncu launches rc=$?"; tail -4 gpurun_out/launches_r2a.csv
-timeout 1500 ncu --set full --clock-control none --import-source on -k regex:decode_mega --launch-skip 4089 --launch-count 1 -o gpurun_out/mega_logits4089_full -f $B > gpurun_out/ncu_full.log 2>&1; echo "ncu full rc=$?"; tail -2 gpurun_out/ncu_full.log
+timeout 1500 ncu --set full --clock-control none -k regex:decode_mega --launch-skip 4089 --launch-count 1 -o gpurun_out/mega_logits4089_full -f $B > gpurun_out/ncu_full.log 2>&1; echo "ncu full rc=$?"; tail -2 gpurun_out/ncu_full.log
 timeout 600 python tools/mega_profile.py --pos 4000 --out gpurun_out/r2a_mega_phase_profile.txt > gpurun_out/phase.log 2>&1; echo "phase rc=$?"; cat gpurun_out/r2a_mega_phase_profile.txt

@@ -37,19 +37,6 @@ def main():
     tot = sum(v for _, v in st)
     for k, v in sorted(st, key=lambda x: -x[1]):
         lines.append(f"{k.replace('smsp__pcsamp_warps_issue_stalled_', ''):28s} {v:8d} {100.0 * v / max(tot, 1):6.1f}%")
-    src = page(rep, "source")
-    if len(src) > 2:
-        hh = src[1]
-        ix = {k: i for i, k in enumerate(hh)}
-        rows = []
-        for r in src[2:]:
-            try:
-                rows.append((int(r[ix["# Samples"]] or 0), int(r[ix["Instructions Executed"]] or 0), r[ix["Source"]]))
-            except (ValueError, IndexError):
-                continue
-        lines.append(f"## hottest SASS instructions by samples (of {sum(r[0] for r in rows)} samples, {len(rows)} instructions)")
-        for s, e, t in sorted(rows, key=lambda x: -x[0])[:25]:
-            lines.append(f"{s:8d} samples {e:12d} exec  {t.strip()[:100]}")
     open(dst, "w").write("\n".join(lines) + "\n")
     print("\n".join(lines[:40]))
 
