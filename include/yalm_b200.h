@@ -29,6 +29,7 @@ extern "C" {
 /* Weight element types; values are the reference's DType enum (src/codec.h:15-25). */
 #define YALM_F32 0
 #define YALM_F16 1
+#define YALM_BF16 2 /* layered architectures (checkpoint directories); the .yalm kernels do not take it */
 #define YALM_F8E5M2 3 /* parsed, but no arithmetic exists for it: rejected */
 #define YALM_F8E4M3 4 /* net-new: e4m3 codes + one fp32 scale per output row */
 
@@ -170,6 +171,52 @@ int yalm_gemm_glu_f16(void *h, int ldh, const void *a, const void *w1, const voi
 int yalm_attn_prefill(void *out16, const void *q16, const uint16_t *key_cache, const uint16_t *value_cache, int n, int pos0,
                       int n_heads, int n_kv_heads, int head_dim, int max_seq_len, yalm_stream_t s);
 
+/* ---- (2c) row-batched ops of the layered executor (no reference counterpart: the reference has one homogeneous
+ * Llama-style block) -------------------------------------------------------------------------------------------------
+ * Every op takes n rows = n consecutive positions of one sequence; n = 1 is a decode step.  Device pointers; fp32
+ * activations; weights fp32 / fp16 / bf16 (out, in) row-major.  Position of row m: pos0 + m, or ctl[1] + m when a device
+ * control block is given.  Key / value rings are head-major (kv head, slot, channel), slot = position % ring, fp32
+ * (cache_f32 != 0) or bf16; pooled keys / values are fp32 (kv head, block, channel). */
+int yalm_embed_rows(float *x, const void *table, const void *positions, int dtype, const int *tokens, int n, int dim, int pos0,
+                    const int *ctl, yalm_stream_t s);
+int yalm_linear_rows(float *y, int ldy, const float *x, int ldx, const void *w, int dtype, int M, int N, int K, float alpha,
+                     yalm_stream_t s);
+int yalm_cast_rows16(void *out16, const float *x, int ldx, int M, int K, int bf16, yalm_stream_t s);
+/* yalm_gemm_f16 with fp16 or bf16 operands and c = alpha * (a w^T) [+ c]. */
+int yalm_gemm_16(float *c, int ldc, const void *a, const void *w, int M, int N, int K, int accumulate, int bf16, float alpha,
+                 yalm_stream_t s);
+/* q | k | v rows (fp32, row stride ld): RMS norm over the whole q and k projections (weights qnorm / knorm, null: none),
+ * vmode 0 plain values, 1 also kept in vfirst, 2 blended v = (1 - vmix[0]) v + vmix[0] vfirst; k and v appended to the rings. */
+int yalm_qkv_post_rows(float *qkv, int ld, void *key_ring, void *value_ring, float *vfirst, int ldvf, const float *qnorm,
+                       const float *knorm, const float *vmix, int vmode, int n, int n_heads, int n_kv, int dk, int dv, int ring,
+                       float eps, int cache_f32, int pos0, const int *ctl, yalm_stream_t s);
+/* Mean key / value of every block of `pool` positions whose last position is one of these rows. */
+int yalm_kv_pool_rows(float *key_pool, float *value_pool, const void *key_ring, const void *value_ring, int n, int n_kv, int dk, int dv,
+                      int ring, int pool, int max_blocks, int cache_f32, int pos0, const int *ctl, yalm_stream_t s);
+/* Attention of n query rows: position i sees tokens j with 0 <= i - j < window (window 0: all) and, if pool > 0, block b
+ * (positions b pool .. b pool + pool - 1) once b pool + pool - 1 <= i - window; one softmax over both; score = q . k * scale. */
+int yalm_attn_window_pool(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring,
+                          const float *key_pool, const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring,
+                          int max_blocks, int window, int pool, float scale, int cache_f32, int pos0, const int *ctl, yalm_stream_t s);
+/* x[m] += rms(sum_{j < nsum} y[m * nsum + j]) * (w_offset + w) */
+int yalm_norm_residual_rows(float *x, const float *y, int ldy, int nsum, const float *w, float w_offset, float eps, int n, int dim,
+                            yalm_stream_t s);
+int yalm_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, float w_offset, float eps, int n_rows, int dim,
+                          yalm_stream_t s);
+/* h[m, f] = act(g) * (u + up_offset), g = gu[m, f], u = gu[m, ff + f]; limit > 0: g = min(g, limit), u clamped to +-limit.
+ * act: YALM_ACT_GELU, YALM_ACT_SILU, 2 = g * sigmoid(alpha g). */
+int yalm_glu_act_rows(float *h, const float *gu, int n, int ff, int act, float alpha, float limit, float up_offset, yalm_stream_t s);
+/* ids / wts (n, top): the experts with the largest scores (score 0: softmax, 1: sigmoid of the fp32 router logits) and
+ * their scores, divided by their sum if renorm. */
+int yalm_router_topk_rows(int *ids, float *wts, const float *x, int ldx, const void *wr, int dtype, int n, int n_experts, int top, int dim,
+                          int score, int renorm, yalm_stream_t s);
+/* Slot s = (row s / top, expert ids[s]) through stacked expert matrices gate / up (E, ff, dim) and down (E, dim, ff);
+ * in_scale: the slot's weight multiplies the expert's input; out_scale: its output. */
+int yalm_moe_glu_slots(float *h, const float *x, int ldx, const void *wg, const void *wu, int dtype, const int *ids, const float *wts, int n,
+                       int top, int ff, int dim, int act, float alpha, float limit, float up_offset, int in_scale, yalm_stream_t s);
+int yalm_moe_down_slots(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top, int ff,
+                        int dim, int out_scale, yalm_stream_t s);
+
 /* ---- (3a) host-pointer test entry points (src/infer.cu:890-1007 semantics) ------------------- */
 int yalm_matmul_host(float *xout, const float *x, const void *w, const float *scale, int n, int d, int dtype);
 int yalm_mha_host(float *xout, float *att, const uint16_t *kb, const uint16_t *vb, const float *q, int head_dim,
@@ -195,6 +242,13 @@ typedef struct yalm_state yalm_state;
 int yalm_model_open_file(const char *path, int context, yalm_model **out);
 /* Image must stay valid until yalm_model_cuda() has returned. */
 int yalm_model_open_memory(const void *image, size_t size, int context, yalm_model **out);
+/* A checkpoint directory (config.json + model.safetensors) of a registered layered architecture.  compute_dtype:
+ * YALM_F32 = everything in true 32-bit (16-bit weights are widened at load), YALM_BF16 / YALM_F16 = 16-bit matrix operands
+ * with fp32 accumulation, negative = as stored.  yalm_model_open_file on a directory is this with compute_dtype -1.
+ * context: most positions a sequence may reach (0: the model's own limit). */
+int yalm_model_open_dir(const char *path, int context, int compute_dtype, yalm_model **out);
+/* 1 for a layered architecture, 0 for a .yalm model. */
+int yalm_model_is_stack(const yalm_model *m);
 /* Tensor-parallel shard `tp_rank` of `tp_size` (1 = whole model) is uploaded to `device`. */
 int yalm_model_cuda(yalm_model *m, int device, int tp_rank, int tp_size);
 void yalm_model_close(yalm_model *m);
@@ -224,6 +278,15 @@ int yalm_generate_greedy(yalm_model *m, yalm_state *s, int token, int pos, int n
  * unsharded models have — and the caller walks the tokens with yalm_forward); pos0 + n <= max_seq_len (no ring wrap). */
 int yalm_model_batch_capacity(const yalm_model *m);
 int yalm_forward_batch(yalm_model *m, yalm_state *s, const int *tokens, int n, int pos0, const int *targets, float *probs_out);
+/* The general step: positions pos0 .. pos0 + n - 1 (n = 1: decode; larger: a portion of a prompt cut anywhere) from the
+ * cache earlier steps left; logits of rows want[0 .. n_want) (ascending row indices) go to logits_out (host, n_want x
+ * vocab).  Layered models take any n in one call; .yalm models walk the rows with yalm_forward. */
+int yalm_forward_rows(yalm_model *m, yalm_state *s, const int *tokens, int n, int pos0, const int *want, int n_want, float *logits_out);
+/* The current sequence is finished: what it holds in the cache is given back; the next step starts at position 0. */
+int yalm_sequence_end(yalm_model *m, yalm_state *s);
+/* Layered models, tests: fp32 copy of layer's key ring (0), value ring (1), pooled keys (2), pooled values (3); and the ring's slot count. */
+int yalm_stack_read(yalm_model *m, int layer, int which, float *dst, size_t count);
+int yalm_stack_ring_slots(const yalm_model *m, int layer);
 /* The same loop with Sampler::sample on the device: temperature 0 = greedy, > 0 = one draw per step with
  * r = uniform(seed, step).  4 bytes per token come back (the reference moves vocab * 4, src/model.cpp:338). */
 int yalm_generate(yalm_model *m, yalm_state *s, int token, int pos, int n_gen, float temperature,

@@ -12,9 +12,10 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("YALM_B200_LIB") or os.path.join(_HERE, "libyalm_b200.so")  # override: A/B builds
+# override: A/B builds, or the core library (`make core`: no whole-token kernel), which is all a layered model needs
+LIB_PATH = os.environ.get("YALM_B200_LIB") or os.path.join(_HERE, "libyalm_b200.so")
 
-F32, F16, F8E4M3 = 0, 1, 4
+F32, F16, BF16, F8E4M3 = 0, 1, 2, 4
 ACT_GELU, ACT_SILU = 0, 1
 MODE_HYDRATE, MODE_LOGITS = 0, 1
 DTYPE_OF = {"fp32": F32, "fp16": F16, "fp8": F8E4M3}
@@ -33,6 +34,9 @@ SYMBOLS = [
     "yalm_profile_ffn", "yalm_sample_advance", "yalm_sample_device1", "yalm_token_probs", "yalm_sample_host",
     "yalm_token_probs_host", "yalm_gemm_f16", "yalm_gemm_glu_f16", "yalm_attn_prefill", "yalm_gemm_host",
     "yalm_model_batch_capacity", "yalm_forward_batch", "yalm_generate", "yalm_state_debug_set_launch_seq", "yalm_tokenize", "yalm_detokenize",
+    "yalm_embed_rows", "yalm_linear_rows", "yalm_cast_rows16", "yalm_gemm_16", "yalm_qkv_post_rows", "yalm_kv_pool_rows", "yalm_attn_window_pool",
+    "yalm_norm_residual_rows", "yalm_norm_gather_rows", "yalm_glu_act_rows", "yalm_router_topk_rows", "yalm_moe_glu_slots", "yalm_moe_down_slots",
+    "yalm_model_open_dir", "yalm_model_is_stack", "yalm_forward_rows", "yalm_sequence_end", "yalm_stack_read", "yalm_stack_ring_slots",
     "yalm_tp_unique_id", "yalm_tp_init", "yalm_tp_finalize", "yalm_tp_shard_plan", "yalm_mega_tile_plan", "yalm_mega_attn_split", "yalm_mega_mma_plan", "yalm_mega_hb_share", "yalm_error_string", "yalm_version",
 ]
 
@@ -64,6 +68,12 @@ def lib():
     L.yalm_bench_op.argtypes = [C.c_char_p, i, i, C.POINTER(C.c_double), C.POINTER(C.c_double)]
     L.yalm_model_open_file.argtypes = [C.c_char_p, i, C.POINTER(vp)]
     L.yalm_model_open_memory.argtypes = [vp, sz, i, C.POINTER(vp)]
+    L.yalm_model_open_dir.argtypes = [C.c_char_p, i, i, C.POINTER(vp)]
+    L.yalm_model_is_stack.argtypes = [vp]
+    L.yalm_forward_rows.argtypes = [vp, vp, vp, i, i, vp, i, vp]
+    L.yalm_sequence_end.argtypes = [vp, vp]
+    L.yalm_stack_read.argtypes = [vp, i, i, vp, sz]
+    L.yalm_stack_ring_slots.argtypes = [vp, i]
     L.yalm_model_cuda.argtypes = [vp, i, i, i]
     L.yalm_model_close.argtypes = [vp]
     L.yalm_model_close.restype = None
@@ -216,10 +226,14 @@ def bench_op(name: str, iters: int = 20, warmup: int = 3):
 class Model:
     """yalm's `Model` (src/model.h:303-327) behind an opaque handle."""
 
-    def __init__(self, yalm, context: int = 0):
+    def __init__(self, yalm, context: int = 0, compute_dtype: int = -1):
+        """`yalm`: a .yalm path, a .yalm image in memory, or a checkpoint directory (config.json + model.safetensors) of a
+        layered architecture; for the latter compute_dtype picks F32 (true 32-bit) or BF16 / F16 operands (-1: as stored)."""
         h = C.c_void_p()
         self._image = None
-        if isinstance(yalm, str):
+        if isinstance(yalm, str) and os.path.isdir(yalm):
+            _check(lib().yalm_model_open_dir(yalm.encode(), context, compute_dtype, C.byref(h)), "Model(directory)")
+        elif isinstance(yalm, str):
             _check(lib().yalm_model_open_file(yalm.encode(), context, C.byref(h)), "Model(file)")
         else:
             self._image = np.frombuffer(yalm, dtype=np.uint8)   # keep alive until cuda()
@@ -251,6 +265,18 @@ class Model:
 
     def batch_capacity(self) -> int:
         return lib().yalm_model_batch_capacity(self.h)
+
+    def is_stack(self) -> bool:
+        return bool(lib().yalm_model_is_stack(self.h))
+
+    def ring_slots(self, layer: int) -> int:
+        return lib().yalm_stack_ring_slots(self.h, layer)
+
+    def stack_read(self, layer: int, which: int, count: int) -> np.ndarray:
+        """Layered models: fp32 copy of a layer's key ring (0), value ring (1), pooled keys (2) or pooled values (3)."""
+        out = np.empty(count, np.float32)
+        _check(lib().yalm_stack_read(self.h, layer, which, _p(out), count), "stack_read")
+        return out
 
     def uses_megakernel(self) -> bool:
         return bool(lib().yalm_model_uses_megakernel(self.h))
@@ -309,6 +335,20 @@ class InferenceState:
         probs = None if targets is None else np.zeros(len(tokens), np.float32)
         _check(lib().yalm_forward_batch(self.model.h, self.h, _p(tokens), len(tokens), pos0, _p(tg), _p(probs)), "forward_batch")
         return probs
+
+    def forward_rows(self, tokens, pos0: int, want=()):
+        """The general step: positions pos0 .. pos0 + len(tokens) - 1 from the cache earlier steps left; returns the logits
+        of the rows in `want` (ascending indices into `tokens`), shape (len(want), vocab)."""
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        want = np.ascontiguousarray(want, np.int32)
+        out = np.zeros((len(want), self.model.vocab_size), np.float32)
+        _check(lib().yalm_forward_rows(self.model.h, self.h, _p(tokens), len(tokens), pos0, _p(want) if len(want) else None, len(want),
+                                       _p(out) if len(want) else None), "forward_rows")
+        return out
+
+    def end_sequence(self):
+        """The sequence is finished; the next step starts at position 0."""
+        _check(lib().yalm_sequence_end(self.model.h, self.h), "end_sequence")
 
     def generate_sampled(self, token: int, pos: int, n_gen: int, temperature: float, seed: int = 0):
         """n_gen steps with Sampler::sample on the device (temperature 0 = greedy); only token ids come back."""

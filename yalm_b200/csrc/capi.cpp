@@ -5,6 +5,8 @@
 
 #include <cuda_runtime.h>
 
+#include <sys/stat.h>
+
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
@@ -276,14 +278,64 @@ static int open_common(yalm_model *h, int context, yalm_model **out) {
 	return 0;
 }
 
+extern "C" int yalm_model_open_dir(const char *path, int context, int compute_dtype, yalm_model **out) {
+	if (!path || !out) return YALM_EINVAL;
+	auto *h = new yalm_model();
+	if (h->data.from_directory(path) != 0) {
+		delete h;
+		return YALM_EFORMAT;
+	}
+	{ // the registry must know the architecture and the reader must accept the configuration before anything is built
+		Config probe;
+		if (probe.from_json(h->data, context, compute_dtype) != 0) {
+			delete h;
+			return YALM_EFORMAT;
+		}
+	}
+	h->model = std::make_unique<Model>(h->data, context, compute_dtype);
+	*out = h;
+	return 0;
+}
+
+extern "C" int yalm_model_is_stack(const yalm_model *m) {
+	return m && m->model->is_stack() ? 1 : 0;
+}
+
+extern "C" int yalm_forward_rows(yalm_model *m, yalm_state *s, const int *tokens, int n, int pos0, const int *want, int n_want, float *logits_out) {
+	if (!m || !s) return YALM_EINVAL;
+	return m->model->forward_rows(*s->state, tokens, n, pos0, want, n_want, logits_out);
+}
+
+extern "C" int yalm_sequence_end(yalm_model *m, yalm_state *s) {
+	if (!m || !s) return YALM_EINVAL;
+	m->model->end_sequence(*s->state);
+	return 0;
+}
+
+extern "C" int yalm_stack_read(yalm_model *m, int layer, int which, float *dst, size_t count) {
+	return m ? m->model->stack_read(layer, which, dst, count) : YALM_EINVAL;
+}
+
+extern "C" int yalm_stack_ring_slots(const yalm_model *m, int layer) {
+	return m ? m->model->stack_ring_slots(layer) : YALM_EINVAL;
+}
+
+static bool is_directory(const char *path);
+
 extern "C" int yalm_model_open_file(const char *path, int context, yalm_model **out) {
 	if (!path || !out) return YALM_EINVAL;
+	if (is_directory(path)) return yalm_model_open_dir(path, context, -1, out);
 	auto *h = new yalm_model();
 	if (h->data.from_file(path) != 0) {
 		delete h;
 		return YALM_EFORMAT;
 	}
 	return open_common(h, context, out);
+}
+
+static bool is_directory(const char *path) {
+	struct stat st;
+	return stat(path, &st) == 0 && S_ISDIR(st.st_mode);
 }
 
 extern "C" int yalm_model_open_memory(const void *image, size_t size, int context, yalm_model **out) {

@@ -240,6 +240,19 @@ int YALMData::from_file(const std::string &filename) {
 	return 0;
 }
 
+int YALMData::from_directory(const std::string &dir) {
+	const std::string cfg = dir + "/config.json";
+	FILE *f = fopen(cfg.c_str(), "rb");
+	if (!f) return -1;
+	char buf[4096];
+	size_t n;
+	config_json.clear();
+	while ((n = fread(buf, 1, sizeof(buf), f)) > 0) config_json.append(buf, n);
+	fclose(f);
+	if (config_json.empty()) return -1;
+	return from_file(dir + "/model.safetensors");
+}
+
 int YALMData::from_memory(const void *image, size_t bytes) {
 	data = const_cast<void *>(image);
 	size = bytes;

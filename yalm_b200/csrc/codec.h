@@ -54,6 +54,10 @@ struct YALMData {
 	int from_file(const std::string &filename);
 	// Parse an image that lives in caller-owned memory (not copied, not freed).
 	int from_memory(const void *image, size_t bytes);
+	// A checkpoint directory: config.json (kept verbatim in config_json; the model registry reads it) beside
+	// model.safetensors, which is the same container as a .yalm file (tensors may be bf16; a shape may be empty: a scalar).
+	int from_directory(const std::string &dir);
+	std::string config_json;
 
 	const Tensor *find(const std::string &name) const {
 		auto it = tensors.find(name);

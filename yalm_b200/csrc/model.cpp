@@ -2,6 +2,7 @@
 // op sequencing and CUDA-graph capture.  See yalm_api.h for how this maps onto the reference API.
 #include "yalm_api.h"
 
+#include "arch.h"
 #include "loader.h"
 #include "mega.h"
 #include "tp.h"
@@ -97,6 +98,23 @@ void Config::from_yalm(YALMData &yalm, int context) {
 
 size_t Config::active_bytes(size_t pos) const {
 	const size_t ws = dtype_size(weight_dtype);
+	if (stack) {
+		// layered model: every layer's own matrices (the selected experts only), its window of keys / values and its pooled blocks
+		const yalm::StackSpec &s = *stack;
+		const size_t W = s.width, cb = weight_dtype == DType::F32 ? 4 : 2;
+		size_t total = 2 * W * ws + (size_t)s.vocab * W * ws + W * 4;
+		for (const yalm::LayerSpec &l : s.layers) {
+			const yalm::MixerSpec &m = l.mix;
+			const size_t nq = (size_t)m.heads * m.dim, nk = (size_t)m.kv_heads * m.dim, nv = (size_t)m.kv_heads * m.vdim, no = (size_t)m.heads * m.vdim;
+			total += (nq + nk + nv + no) * W * ws + (nq + nk + 2 * W) * 4;
+			const size_t seen = m.window > 0 ? std::min<size_t>(pos + 1, m.window) : pos + 1;
+			const size_t blocks = (m.window > 0 && m.pool > 0 && pos + 1 >= (size_t)m.window + m.pool) ? (pos + 1 - m.window) / m.pool : 0;
+			total += seen * (nk + nv) * cb + blocks * (nk + nv) * 4;
+			if (l.ffn.kind == yalm::FfnSpec::Dense) total += (size_t)3 * l.ffn.ff * W * ws;
+			else if (l.ffn.kind == yalm::FfnSpec::Moe) total += ((size_t)l.ffn.experts * W + (size_t)l.ffn.top * 3 * l.ffn.ff * W) * ws;
+		}
+		return total;
+	}
 	const size_t q_dim = (size_t)n_heads * head_dim, kv_dim = (size_t)n_kv_heads * head_dim;
 	size_t per_block = 2 * (size_t)dim * sizeof(float);
 	per_block += (2 * q_dim + 2 * kv_dim) * dim * ws;
@@ -528,8 +546,18 @@ void Block::block(InferenceState &s, int pos, int kv_sink, int kv_pos, int kv_le
 // ------------------------------------------------------------------------------------------------
 // Model
 // ------------------------------------------------------------------------------------------------
-Model::Model(YALMData &yalm, int context) {
+Model::Model(YALMData &yalm, int context, int compute_dtype) {
 	config = std::make_shared<Config>();
+	if (!yalm.config_json.empty()) { // a checkpoint directory: the model registry picks the layered architecture's reader
+		if (config->from_json(yalm, context, compute_dtype) != 0) {
+			std::cerr << "FATAL: unusable config.json" << std::endl;
+			abort();
+		}
+		std::cout << "loading " << config->stack->arch << " model, " << config->n_layers << " layers, computing in " << dtype_to_string(config->weight_dtype)
+		          << std::endl;
+		build_stack(yalm);
+		return;
+	}
 	config->from_yalm(yalm, context);
 	const Config &c = *config;
 	std::cout << "loading model with dtype: " << dtype_to_string(c.weight_dtype) << std::endl;
@@ -581,6 +609,14 @@ void Model::cuda() {
 void Model::cuda(int device, int tp_rank, int tp_size) {
 	if (_device != Device::CPU) return;
 	Config &c = *config;
+	if (c.stack) {
+		if (tp_size != 1) {
+			std::cerr << "FATAL: layered models run on one GPU" << std::endl;
+			abort();
+		}
+		cuda_stack(device);
+		return;
+	}
 	const yalm::TpDims td{c.dim, c.hidden_dim, c.head_dim, c.n_heads, c.n_kv_heads, c.vocab_size, (int)dtype_size(c.weight_dtype)};
 	if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size || !yalm::tp_shards(td, tp_size)) {
 		std::cerr << "FATAL: model does not shard " << tp_size << " ways (kv heads " << c.n_kv_heads << ", hidden "
@@ -779,6 +815,11 @@ int Model::launch_mega(InferenceState &s, int token, int pos, int mode, long lon
 }
 
 int Model::launches_per_forward(InferenceMode mode) const {
+	if (config->stack) { // embed + per layer: qkv, q/k norm + append, [pool], attention, wo, norm + residual, feed-forward (4) [+ final norm, head]
+		int n = 1;
+		for (const yalm::LayerSpec &l : config->stack->layers) n += 5 + (l.mix.pool > 0 ? 1 : 0) + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 4);
+		return n + (mode == InferenceMode::OUTPUT_LOGITS ? 2 : 0);
+	}
 	if (_mega_ok) return 1;
 	// embed + 5 kernels per block (qkv+rope+append, flash-decode, wo+res, ffn-glu, w2+res) [+ lm head]
 	// (+ 2 NCCL all-reduce kernels per block and one all-gather under tensor parallelism)
@@ -835,6 +876,11 @@ void Model::forward(InferenceState &s, int token, int pos, InferenceMode mode) {
 		abort();
 	}
 	s.set_mode(mode);
+	if (c.stack) { // layered model: one row through the general step
+		const int row = 0;
+		OP_CHECK(stack_rows(s, &token, 1, pos, &row, mode == InferenceMode::OUTPUT_LOGITS ? 1 : 0, nullptr, nullptr, nullptr));
+		return;
+	}
 	if (_mega_ok) {
 		// one persistent kernel per token; token / pos travel as kernel arguments
 		OP_CHECK(launch_mega(s, token, pos,
@@ -890,6 +936,7 @@ int Model::generate(InferenceState &s, int token, int pos, int n_gen, float temp
                     int *tokens_out, float *logits_out, float *device_ms) {
 	if (_device != Device::CUDA || s.device() != Device::CUDA) return YALM_ENOGPU;
 	const Config &c = *config;
+	if (c.stack) return stack_generate(s, token, pos, n_gen, temperature, seed, tokens_out, logits_out, device_ms);
 	if (n_gen < 1 || n_gen > s.tokens_capacity() || token < 0 || token >= c.vocab_size || pos < 0 || !tokens_out ||
 	    !(temperature >= 0.f))
 		return YALM_EINVAL;

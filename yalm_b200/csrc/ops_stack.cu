@@ -1,0 +1,658 @@
+// Row-batched ops of the layered executor (stack.cpp): every op takes M rows = M consecutive positions of one sequence,
+// M = 1 being a decode step and M > 1 a portion of a prompt, so that both run the same arithmetic.  The residual stream,
+// norms, scores, softmax weights and router are fp32 whatever the weight type; weights are fp32 / fp16 / bf16 (out, in)
+// row-major and every product accumulates in fp32.
+//
+// Mechanisms (each with its constants as parameters, so another layered design can use them):
+//   embed_rows            x = E[token] (+ learned position row)
+//   linear_rows           y = alpha * x W^T: warp-per-output GEMV for few rows, 64 x 64 SIMT tiles for many (the tensor-core
+//                         route for 16-bit weights is prefill_gemm.cu; this is the exact-fp32 and odd-shape route)
+//   qkv_post_rows         RMS norm over the whole q / k projection, value blending with an earlier layer's values, append
+//                         to the key / value ring
+//   kv_pool_rows          mean key / value of every token block completed by these rows
+//   attn_window_pool      sliding window + pooled blocks in one softmax
+//   norm_residual_rows    x += rms(sum of partial outputs) * (offset + w)
+//   glu_act_rows          gated activation with clamps and up offset
+//   router_topk_rows      fp32 router, sigmoid / softmax scores, top-k
+//   moe_glu_slots / moe_down_slots   per (row, selected expert) projections through stacked expert matrices
+//   norm_gather_rows      final norm of the rows whose logits are wanted
+// Positions: p0 + row, p0 = ctl[CTL_POS] when a device control block is given (device-side decode loops), else the argument.
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+
+#include "gemv.cuh"
+
+namespace yalm {
+namespace stack {
+
+// ---- element access ----------------------------------------------------------------------------------------------------
+template <int DT> struct Elem;
+template <> struct Elem<YALM_F32> {
+	using T = float;
+	static constexpr int VEC = 4;
+	__device__ static __forceinline__ float get(const void *p, size_t i) { return static_cast<const float *>(p)[i]; }
+	__device__ static __forceinline__ void unpack(uint4 w, float (&f)[8]) {
+		f[0] = __uint_as_float(w.x), f[1] = __uint_as_float(w.y), f[2] = __uint_as_float(w.z), f[3] = __uint_as_float(w.w);
+	}
+};
+template <> struct Elem<YALM_F16> {
+	using T = __half;
+	static constexpr int VEC = 8;
+	__device__ static __forceinline__ float get(const void *p, size_t i) { return __half2float(static_cast<const __half *>(p)[i]); }
+	__device__ static __forceinline__ void unpack(uint4 w, float (&f)[8]) {
+		const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+		for (int i = 0; i < 4; ++i) {
+			const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&u[i]));
+			f[2 * i] = v.x, f[2 * i + 1] = v.y;
+		}
+	}
+};
+template <> struct Elem<YALM_BF16> {
+	using T = __nv_bfloat16;
+	static constexpr int VEC = 8;
+	__device__ static __forceinline__ float get(const void *p, size_t i) {
+		return __uint_as_float((uint32_t) static_cast<const uint16_t *>(p)[i] << 16);
+	}
+	__device__ static __forceinline__ void unpack(uint4 w, float (&f)[8]) { // bf16 -> fp32 is a 16-bit shift
+		const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+		for (int i = 0; i < 4; ++i) f[2 * i] = __uint_as_float(u[i] << 16), f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+	}
+};
+
+__device__ __forceinline__ float cache_get(const float *p, size_t i) { return p[i]; }
+__device__ __forceinline__ float cache_get(const __nv_bfloat16 *p, size_t i) {
+	return __uint_as_float((uint32_t) reinterpret_cast<const uint16_t *>(p)[i] << 16);
+}
+__device__ __forceinline__ void cache_put(float *p, size_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void cache_put(__nv_bfloat16 *p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ int first_pos(const int *ctl, int pos0) { return ctl ? ctl[CTL_POS] : pos0; }
+
+// dot(weight row, x) over K elements, result in every lane.  `vec`: the row and x are 16-byte aligned and K % VEC == 0.
+template <int DT>
+__device__ __forceinline__ float warp_dot(const void *w, size_t row_off, const float *__restrict__ x, int K, bool vec) {
+	using E = Elem<DT>;
+	const int lane = threadIdx.x & 31;
+	float acc = 0.f;
+	if (vec) {
+		const typename E::T *row = static_cast<const typename E::T *>(w) + row_off;
+		for (int k = lane * E::VEC; k < K; k += 32 * E::VEC) {
+			float f[8];
+			E::unpack(ldg_stream(row + k), f);
+#pragma unroll
+			for (int i = 0; i < E::VEC; i += 4) {
+				const float4 xv = *reinterpret_cast<const float4 *>(x + k + i);
+				acc = fmaf(f[i], xv.x, acc), acc = fmaf(f[i + 1], xv.y, acc), acc = fmaf(f[i + 2], xv.z, acc), acc = fmaf(f[i + 3], xv.w, acc);
+			}
+		}
+	} else {
+		for (int k = lane; k < K; k += 32) acc = fmaf(E::get(w, row_off + k), x[k], acc);
+	}
+	return warp_sum(acc);
+}
+
+__host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---- embedding ---------------------------------------------------------------------------------------------------------
+template <int DT>
+__global__ void embed_rows_kernel(float *__restrict__ x, const void *__restrict__ table, const void *__restrict__ positions,
+                                  const int *__restrict__ tokens, int dim, int pos0, const int *__restrict__ ctl) {
+	const int m = blockIdx.x;
+	const int tok = tokens ? tokens[m] : ctl[CTL_TOKEN];
+	const int p = first_pos(ctl, pos0) + m;
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+		float v = Elem<DT>::get(table, (size_t)tok * dim + e);
+		if (positions) v += Elem<DT>::get(positions, (size_t)p * dim + e);
+		x[(size_t)m * dim + e] = v;
+	}
+}
+
+// ---- linear: few rows ------------------------------------------------------------------------------------------------
+// One warp per output column n, MB rows of x per pass (grid.y walks the passes): the weight row is read once per pass.
+constexpr int kLinMB = 8;
+template <int DT>
+__global__ void __launch_bounds__(256) linear_few_kernel(float *__restrict__ y, int ldy, const float *__restrict__ x, int ldx,
+                                                         const void *__restrict__ w, int M, int N, int K, float alpha, bool vec) {
+	using E = Elem<DT>;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int n = blockIdx.x * 8 + warp;
+	if (n >= N) return;
+	const int m0 = blockIdx.y * kLinMB, mb = min(kLinMB, M - m0);
+	float acc[kLinMB];
+#pragma unroll
+	for (int i = 0; i < kLinMB; ++i) acc[i] = 0.f;
+	const size_t row_off = (size_t)n * K;
+	if (vec) {
+		const typename E::T *row = static_cast<const typename E::T *>(w) + row_off;
+		for (int k = lane * E::VEC; k < K; k += 32 * E::VEC) {
+			float f[8];
+			E::unpack(ldg_stream(row + k), f);
+#pragma unroll
+			for (int i = 0; i < kLinMB; ++i)
+				if (i < mb) {
+					const float *xr = x + (size_t)(m0 + i) * ldx + k;
+#pragma unroll
+					for (int j = 0; j < E::VEC; j += 4) {
+						const float4 xv = *reinterpret_cast<const float4 *>(xr + j);
+						acc[i] = fmaf(f[j], xv.x, acc[i]), acc[i] = fmaf(f[j + 1], xv.y, acc[i]);
+						acc[i] = fmaf(f[j + 2], xv.z, acc[i]), acc[i] = fmaf(f[j + 3], xv.w, acc[i]);
+					}
+				}
+		}
+	} else {
+		for (int k = lane; k < K; k += 32) {
+			const float wv = E::get(w, row_off + k);
+#pragma unroll
+			for (int i = 0; i < kLinMB; ++i)
+				if (i < mb) acc[i] = fmaf(wv, x[(size_t)(m0 + i) * ldx + k], acc[i]);
+		}
+	}
+#pragma unroll
+	for (int i = 0; i < kLinMB; ++i) {
+		const float s = warp_sum(acc[i]);
+		if (i < mb && lane == 0) y[(size_t)(m0 + i) * ldy + n] = alpha * s;
+	}
+}
+
+// ---- linear: many rows, SIMT tiles -----------------------------------------------------------------------------------
+// 64 x 64 output tile per CTA, K in steps of 16, 256 threads x (4 x 4) outputs.  Operands are staged transposed
+// ([k][row]) so that the inner product reads float4s; edges are zero-filled.  fp32 multiply-add throughout: this is the
+// route of the exact-fp32 mode and of shapes the tensor-core GEMM's 16-byte row rule excludes.
+template <int DT>
+__global__ void __launch_bounds__(256) linear_tiled_kernel(float *__restrict__ y, int ldy, const float *__restrict__ x, int ldx,
+                                                           const void *__restrict__ w, int M, int N, int K, float alpha) {
+	using E = Elem<DT>;
+	__shared__ __align__(16) float As[16][64 + 4], Ws[16][64 + 4];
+	const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+	const int tid = threadIdx.x, tm = tid >> 4, tn = tid & 15;
+	const int lr = tid >> 2, lk = (tid & 3) * 4; // this thread stages row lr, k offsets lk .. lk + 3 of both operands
+	float acc[4][4];
+#pragma unroll
+	for (int i = 0; i < 4; ++i)
+#pragma unroll
+		for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+	for (int k0 = 0; k0 < K; k0 += 16) {
+		float a[4], b[4];
+#pragma unroll
+		for (int i = 0; i < 4; ++i) {
+			const int k = k0 + lk + i;
+			a[i] = (m0 + lr < M && k < K) ? x[(size_t)(m0 + lr) * ldx + k] : 0.f;
+			b[i] = (n0 + lr < N && k < K) ? E::get(w, (size_t)(n0 + lr) * K + k) : 0.f;
+		}
+		__syncthreads(); // the previous step's reads are done
+#pragma unroll
+		for (int i = 0; i < 4; ++i) As[lk + i][lr] = a[i], Ws[lk + i][lr] = b[i];
+		__syncthreads();
+#pragma unroll
+		for (int k = 0; k < 16; ++k) {
+			const float4 av = *reinterpret_cast<const float4 *>(&As[k][tm * 4]), bv = *reinterpret_cast<const float4 *>(&Ws[k][tn * 4]);
+			const float aa[4] = {av.x, av.y, av.z, av.w}, bb[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+			for (int i = 0; i < 4; ++i)
+#pragma unroll
+				for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(aa[i], bb[j], acc[i][j]);
+		}
+	}
+#pragma unroll
+	for (int i = 0; i < 4; ++i) {
+		const int m = m0 + tm * 4 + i;
+		if (m >= M) continue;
+#pragma unroll
+		for (int j = 0; j < 4; ++j) {
+			const int n = n0 + tn * 4 + j;
+			if (n < N) y[(size_t)m * ldy + n] = alpha * acc[i][j];
+		}
+	}
+}
+
+// fp32 rows -> 16-bit rows (the A operand of the tensor-core GEMM), K padded columns are not written
+template <typename T>
+__global__ void cast_rows_kernel(T *__restrict__ out, const float *__restrict__ x, int ldx, int K) {
+	const float *row = x + (size_t)blockIdx.x * ldx;
+	T *dst = out + (size_t)blockIdx.x * K;
+	for (int e = threadIdx.x; e < K; e += blockDim.x) dst[e] = T(row[e]);
+}
+
+// ---- q / k norm, value blending, cache append ---------------------------------------------------------------------------
+// Row m of qkv (fp32, q | k | v, ld) is position p0 + m.  q and k: RMS norm over the WHOLE projection (all heads at once),
+// one weight per channel (qnorm / knorm null: left as they are); q stays in place, k goes to the ring.  v: vmode 1 keeps a
+// copy in vfirst (the first blending layer), vmode 2 blends v = (1 - lambda) v + lambda vfirst (later blending layers);
+// the blended v is what is cached.  Ring slot of position p: p % ring; caches are head-major (kv head, slot, channel).
+template <typename CT>
+__global__ void __launch_bounds__(256) qkv_post_rows_kernel(float *__restrict__ qkv, int ld, CT *__restrict__ kc, CT *__restrict__ vc,
+                                                            float *__restrict__ vfirst, int ldvf, const float *__restrict__ qnorm,
+                                                            const float *__restrict__ knorm, const float *__restrict__ vmix, int vmode, int nq,
+                                                            int nk, int nv, int dk, int dv, int ring, float eps, int pos0,
+                                                            const int *__restrict__ ctl) {
+	__shared__ float red[33];
+	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m, slot = p % ring;
+	float *row = qkv + (size_t)m * ld;
+	float rq = 1.f, rk = 1.f;
+	if (qnorm) {
+		float s = 0.f;
+		for (int e = threadIdx.x; e < nq; e += blockDim.x) s += row[e] * row[e];
+		s = block_sum(s, red);
+		rq = 1.0f / sqrtf(s / nq + eps);
+	}
+	if (knorm) {
+		float s = 0.f;
+		for (int e = threadIdx.x; e < nk; e += blockDim.x) s += row[nq + e] * row[nq + e];
+		s = block_sum(s, red);
+		rk = 1.0f / sqrtf(s / nk + eps);
+	}
+	if (qnorm)
+		for (int e = threadIdx.x; e < nq; e += blockDim.x) row[e] = row[e] * rq * qnorm[e];
+	for (int e = threadIdx.x; e < nk; e += blockDim.x) {
+		float v = row[nq + e];
+		if (knorm) v = v * rk * knorm[e];
+		const int g = e / dk, d = e % dk;
+		cache_put(kc, ((size_t)g * ring + slot) * dk + d, v);
+	}
+	const float lam = vmode == 2 ? vmix[0] : 0.f;
+	for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+		float v = row[nq + nk + e];
+		if (vmode == 1) vfirst[(size_t)m * ldvf + e] = v;
+		else if (vmode == 2) v = (1.0f - lam) * v + lam * vfirst[(size_t)m * ldvf + e];
+		const int g = e / dv, d = e % dv;
+		cache_put(vc, ((size_t)g * ring + slot) * dv + d, v);
+	}
+}
+
+// Mean key / value (fp32) of every block of `pool` positions whose last position is one of these rows; the members are read
+// back from the ring, as it holds them.  grid (n / pool + 1, kv heads).
+template <typename CT>
+__global__ void kv_pool_rows_kernel(float *__restrict__ kp, float *__restrict__ vp, const CT *__restrict__ kc, const CT *__restrict__ vc, int n,
+                                    int dk, int dv, int ring, int pool, int max_blocks, int pos0, const int *__restrict__ ctl) {
+	const int p0 = first_pos(ctl, pos0);
+	const int b = p0 / pool + blockIdx.x, g = blockIdx.y; // first block whose end (b * pool + pool - 1) is >= p0
+	if (b * pool + pool > p0 + n || b >= max_blocks) return;
+	const float inv = 1.0f / (float)pool;
+	for (int d = threadIdx.x; d < dk + dv; d += blockDim.x) {
+		float s = 0.f;
+		for (int t = 0; t < pool; ++t) {
+			const int slot = (b * pool + t) % ring;
+			s += d < dk ? cache_get(kc, ((size_t)g * ring + slot) * dk + d) : cache_get(vc, ((size_t)g * ring + slot) * dv + (d - dk));
+		}
+		if (d < dk) kp[((size_t)g * max_blocks + b) * dk + d] = s * inv;
+		else vp[((size_t)g * max_blocks + b) * dv + (d - dk)] = s * inv;
+	}
+}
+
+// ---- attention: sliding window + pooled blocks, one softmax ------------------------------------------------------------
+// Query row m at position i = p0 + m sees the tokens lo .. i (lo = max(0, i - window + 1); window 0: lo = 0) and, when
+// pool > 0, the blocks 0 .. nb - 1 with nb = floor((i - window + 1) / pool): those whose last token has left the window.
+// One CTA per (head, row); its warps take 32-key tiles in turn: lane = key for the scores (each lane walks its own key
+// row), online softmax per warp in fp32, then lane = value channel for P V.  Warps merge in shared memory.
+constexpr int kAttnWarps = 4;
+constexpr int kAttnMaxDvc = 8; // value channels per lane: vdim <= 256
+
+template <typename CT>
+__device__ __forceinline__ float key_dot(const CT *krow, const float *qs, int dk, bool vec);
+template <>
+__device__ __forceinline__ float key_dot<float>(const float *krow, const float *qs, int dk, bool vec) {
+	float s = 0.f;
+	if (vec) {
+		for (int d = 0; d < dk; d += 4) {
+			const float4 kv = *reinterpret_cast<const float4 *>(krow + d), qv = *reinterpret_cast<const float4 *>(qs + d);
+			s = fmaf(kv.x, qv.x, s), s = fmaf(kv.y, qv.y, s), s = fmaf(kv.z, qv.z, s), s = fmaf(kv.w, qv.w, s);
+		}
+	} else
+		for (int d = 0; d < dk; ++d) s = fmaf(krow[d], qs[d], s);
+	return s;
+}
+template <>
+__device__ __forceinline__ float key_dot<__nv_bfloat16>(const __nv_bfloat16 *krow, const float *qs, int dk, bool vec) {
+	float s = 0.f;
+	if (vec) {
+		for (int d = 0; d < dk; d += 8) {
+			float f[8];
+			Elem<YALM_BF16>::unpack(*reinterpret_cast<const uint4 *>(krow + d), f);
+#pragma unroll
+			for (int i = 0; i < 8; ++i) s = fmaf(f[i], qs[d + i], s);
+		}
+	} else
+		for (int d = 0; d < dk; ++d) s = fmaf(cache_get(krow, d), qs[d], s);
+	return s;
+}
+
+template <typename CT>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                                           const CT *__restrict__ kc, const CT *__restrict__ vc,
+                                                                           const float *__restrict__ kp, const float *__restrict__ vp, int n_heads,
+                                                                           int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool,
+                                                                           float scale, int pos0, const int *__restrict__ ctl) {
+	extern __shared__ __align__(16) float sm[];
+	float *qs = sm;                              // dk (padded to 8)
+	float *macc = sm + ((dk + 7) & ~7);          // kAttnWarps x dv
+	float *mml = macc + kAttnWarps * dv;         // kAttnWarps x 2
+	const int h = blockIdx.x, m = blockIdx.y, g = h / (n_heads / n_kv);
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int i = first_pos(ctl, pos0) + m;
+	const int lo = window > 0 ? max(0, i - window + 1) : 0;
+	const int nb = (window > 0 && pool > 0 && i - window + 1 >= pool) ? (i - window + 1) / pool : 0;
+	const int nkeys = nb + (i - lo + 1);
+	for (int d = threadIdx.x; d < dk; d += blockDim.x) qs[d] = q[(size_t)m * ldq + (size_t)h * dk + d] * scale;
+	__syncthreads();
+	const CT *kbase = kc + (size_t)g * ring * dk, *vbase = vc + (size_t)g * ring * dv;
+	const float *kpb = kp ? kp + (size_t)g * max_blocks * dk : nullptr, *vpb = vp ? vp + (size_t)g * max_blocks * dv : nullptr;
+	const bool kvec_c = (dk * sizeof(CT)) % 16 == 0 && aligned16(kbase), kvec_p = (dk * 4) % 16 == 0 && aligned16(kpb);
+	float mx = -INFINITY, l = 0.f, acc[kAttnMaxDvc];
+#pragma unroll
+	for (int c = 0; c < kAttnMaxDvc; ++c) acc[c] = 0.f;
+	for (int t0 = warp * 32; t0 < nkeys; t0 += kAttnWarps * 32) {
+		const int u = t0 + lane;
+		float s = -INFINITY;
+		if (u < nkeys) {
+			if (u < nb) s = key_dot<float>(kpb + (size_t)u * dk, qs, dk, kvec_p);
+			else s = key_dot<CT>(kbase + (size_t)((lo + u - nb) % ring) * dk, qs, dk, kvec_c);
+		}
+		const float tmax = warp_max(s);              // finite: the tile holds at least one key
+		const float nmx = fmaxf(mx, tmax);
+		const float corr = mx == -INFINITY ? 0.f : expf(mx - nmx);
+		const float p = u < nkeys ? expf(s - nmx) : 0.f;
+		l = l * corr + warp_sum(p);
+		mx = nmx;
+#pragma unroll
+		for (int c = 0; c < kAttnMaxDvc; ++c) acc[c] *= corr;
+		const int cnt = min(32, nkeys - t0);
+		for (int kk = 0; kk < cnt; ++kk) {
+			const float pk = __shfl_sync(kFull, p, kk);
+			const int uk = t0 + kk;
+			if (uk < nb) {
+				const float *vr = vpb + (size_t)uk * dv;
+#pragma unroll
+				for (int c = 0; c < kAttnMaxDvc; ++c)
+					if (c * 32 + lane < dv) acc[c] = fmaf(pk, vr[c * 32 + lane], acc[c]);
+			} else {
+				const CT *vr = vbase + (size_t)((lo + uk - nb) % ring) * dv;
+#pragma unroll
+				for (int c = 0; c < kAttnMaxDvc; ++c)
+					if (c * 32 + lane < dv) acc[c] = fmaf(pk, cache_get(vr, c * 32 + lane), acc[c]);
+			}
+		}
+	}
+#pragma unroll
+	for (int c = 0; c < kAttnMaxDvc; ++c)
+		if (c * 32 + lane < dv) macc[warp * dv + c * 32 + lane] = acc[c];
+	if (lane == 0) mml[warp * 2] = mx, mml[warp * 2 + 1] = l;
+	__syncthreads();
+	if (warp == 0) {
+		float M = -INFINITY;
+		for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, mml[w * 2]);
+		float wt[kAttnWarps], L = 0.f;
+		for (int w = 0; w < kAttnWarps; ++w) {
+			wt[w] = mml[w * 2] == -INFINITY ? 0.f : expf(mml[w * 2] - M);
+			L += wt[w] * mml[w * 2 + 1];
+		}
+		for (int c = lane; c < dv; c += 32) {
+			float o = 0.f;
+			for (int w = 0; w < kAttnWarps; ++w) o += wt[w] * macc[w * dv + c];
+			out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+		}
+	}
+}
+
+// ---- x += rms(sum_j y_j) * (offset + w) ------------------------------------------------------------------------------------
+// y holds nsum partial outputs per row (row m, part j at row m * nsum + j): the sum over a row's selected experts in slot
+// order, or the single output of a dense sublayer.  The residual stream is fp32.
+__global__ void __launch_bounds__(256) norm_residual_rows_kernel(float *__restrict__ x, const float *__restrict__ y, int ldy, int nsum,
+                                                                 const float *__restrict__ w, float woff, float eps, int dim) {
+	__shared__ float red[33];
+	extern __shared__ float ys[]; // dim
+	const int m = blockIdx.x;
+	float ss = 0.f;
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+		float v = 0.f;
+		for (int j = 0; j < nsum; ++j) v += y[((size_t)m * nsum + j) * ldy + e];
+		ys[e] = v;
+		ss += v * v;
+	}
+	ss = block_sum(ss, red);
+	const float r = 1.0f / sqrtf(ss / dim + eps);
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) x[(size_t)m * dim + e] += ys[e] * r * (woff + w[e]);
+}
+
+// out[r] = rms(x[rows[r]]) * (offset + w)   (rows null: r itself)
+__global__ void __launch_bounds__(256) norm_gather_rows_kernel(float *__restrict__ out, const float *__restrict__ x, const int *__restrict__ rows,
+                                                               const float *__restrict__ w, float woff, float eps, int dim) {
+	__shared__ float red[33];
+	const int r = blockIdx.x, m = rows ? rows[r] : r;
+	const float *src = x + (size_t)m * dim;
+	float ss = 0.f;
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) ss += src[e] * src[e];
+	ss = block_sum(ss, red);
+	const float s = 1.0f / sqrtf(ss / dim + eps);
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) out[(size_t)r * dim + e] = src[e] * s * (woff + w[e]);
+}
+
+// ---- gated activation ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float glu_value(float g, float u, int act, float alpha, float limit, float up_offset) {
+	if (limit > 0.f) g = fminf(g, limit), u = fminf(fmaxf(u, -limit), limit);
+	float a;
+	if (act == 2) a = g / (1.0f + expf(-alpha * g));      // g * sigmoid(alpha g)
+	else if (act == YALM_ACT_SILU) a = act_silu(g);
+	else a = act_gelu(g);
+	return a * (u + up_offset);
+}
+// h[m, f] = act(gu[m, f]) * (gu[m, ff + f] + up_offset)
+__global__ void glu_act_rows_kernel(float *__restrict__ h, const float *__restrict__ gu, int ff, int act, float alpha, float limit, float up_offset) {
+	const int m = blockIdx.y;
+	const int f = blockIdx.x * blockDim.x + threadIdx.x;
+	if (f >= ff) return;
+	const float *row = gu + (size_t)m * 2 * ff;
+	h[(size_t)m * ff + f] = glu_value(row[f], row[ff + f], act, alpha, limit, up_offset);
+}
+
+// ---- router ----------------------------------------------------------------------------------------------------------
+// z = Wr x (fp32), scores = sigmoid(z) or softmax(z); the `top` largest (ties: the lower index) with their scores as
+// weights, optionally divided by their sum.  One CTA per row; E <= 1024.
+template <int DT>
+__global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ x, int ldx,
+                                                               const void *__restrict__ wr, int E, int top, int dim, int score, int renorm, bool vec) {
+	extern __shared__ float sc[]; // E
+	const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const float *xr = x + (size_t)m * ldx;
+	for (int e = warp; e < E; e += 4) {
+		const float z = warp_dot<DT>(wr, (size_t)e * dim, xr, dim, vec);
+		if (lane == 0) sc[e] = z;
+	}
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		if (score == 1) {
+			for (int e = 0; e < E; ++e) sc[e] = 1.0f / (1.0f + expf(-sc[e]));
+		} else {
+			float mx = -INFINITY, sum = 0.f;
+			for (int e = 0; e < E; ++e) mx = fmaxf(mx, sc[e]);
+			for (int e = 0; e < E; ++e) sc[e] = expf(sc[e] - mx), sum += sc[e];
+			for (int e = 0; e < E; ++e) sc[e] /= sum;
+		}
+		float tot = 0.f;
+		for (int j = 0; j < top; ++j) {
+			int best = -1;
+			float bv = -INFINITY;
+			for (int e = 0; e < E; ++e)
+				if (sc[e] > bv) bv = sc[e], best = e;
+			ids[(size_t)m * top + j] = best, wts[(size_t)m * top + j] = bv;
+			tot += bv;
+			sc[best] = -INFINITY;
+		}
+		if (renorm)
+			for (int j = 0; j < top; ++j) wts[(size_t)m * top + j] /= tot;
+	}
+}
+
+// ---- experts, one (row, selected expert) slot at a time -------------------------------------------------------------------
+// Stacked expert matrices: gate / up (E, ff, dim), down (E, dim, ff).  Slot s = row s / top, expert ids[s], weight wts[s].
+// in_scale: the weight multiplies the expert's input — W (w h) = w (W h), applied to both projections before the
+// activation; otherwise it multiplies the expert's output (moe_down_slots).
+template <int DT>
+__global__ void __launch_bounds__(128) moe_glu_slots_kernel(float *__restrict__ h, const float *__restrict__ x, int ldx, const void *__restrict__ wg,
+                                                            const void *__restrict__ wu, const int *__restrict__ ids, const float *__restrict__ wts,
+                                                            int top, int ff, int dim, int act, float alpha, float limit, float up_offset, int in_scale,
+                                                            bool vec) {
+	const int s = blockIdx.y, f = blockIdx.x * 4 + (threadIdx.x >> 5);
+	if (f >= ff) return;
+	const int e = ids[s];
+	const float *xr = x + (size_t)(s / top) * ldx;
+	const size_t off = ((size_t)e * ff + f) * dim;
+	float a = warp_dot<DT>(wg, off, xr, dim, vec), b = warp_dot<DT>(wu, off, xr, dim, vec);
+	if (in_scale) a *= wts[s], b *= wts[s];
+	if ((threadIdx.x & 31) == 0) h[(size_t)s * ff + f] = glu_value(a, b, act, alpha, limit, up_offset);
+}
+template <int DT>
+__global__ void __launch_bounds__(128) moe_down_slots_kernel(float *__restrict__ y, int ldy, const float *__restrict__ h, const void *__restrict__ wd,
+                                                             const int *__restrict__ ids, const float *__restrict__ wts, int ff, int dim, int out_scale,
+                                                             bool vec) {
+	const int s = blockIdx.y, n = blockIdx.x * 4 + (threadIdx.x >> 5);
+	if (n >= dim) return;
+	const int e = ids[s];
+	float v = warp_dot<DT>(wd, ((size_t)e * dim + n) * ff, h + (size_t)s * ff, ff, vec);
+	if (out_scale) v *= wts[s];
+	if ((threadIdx.x & 31) == 0) y[(size_t)s * ldy + n] = v;
+}
+
+} // namespace stack
+} // namespace yalm
+
+using namespace yalm;
+using namespace yalm::stack;
+
+#define DISPATCH_DT(dtype, CALL)                                                                                                   \
+	switch (dtype) {                                                                                                               \
+	case YALM_F32: { constexpr int DT = YALM_F32; CALL; break; }                                                                  \
+	case YALM_F16: { constexpr int DT = YALM_F16; CALL; break; }                                                                  \
+	case YALM_BF16: { constexpr int DT = YALM_BF16; CALL; break; }                                                                \
+	default: return YALM_EINVAL;                                                                                                   \
+	}
+
+static inline int elem_size(int dtype) { return dtype == YALM_F32 ? 4 : 2; }
+static inline bool row_vec(const void *w, int K, int dtype) { return aligned16(w) && ((size_t)K * elem_size(dtype)) % 16 == 0; }
+
+extern "C" int yalm_embed_rows(float *x, const void *table, const void *positions, int dtype, const int *tokens, int n, int dim, int pos0,
+                               const int *ctl, yalm_stream_t s) {
+	if (!x || !table || n < 1 || dim < 1 || (!tokens && !ctl)) return YALM_EINVAL;
+	DISPATCH_DT(dtype, (embed_rows_kernel<DT><<<n, 256, 0, (cudaStream_t)s>>>(x, table, positions, tokens, dim, pos0, ctl)));
+	return (int)cudaGetLastError();
+}
+
+// y (M, ldy) fp32 = alpha * x (M, ldx) fp32 * w (N, K)^T.  `few` rows: one warp per output column; else SIMT tiles.
+extern "C" int yalm_linear_rows(float *y, int ldy, const float *x, int ldx, const void *w, int dtype, int M, int N, int K, float alpha,
+                                yalm_stream_t s) {
+	if (!y || !x || !w || M < 1 || N < 1 || K < 1 || ldy < N || ldx < K) return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	if (M <= 2 * kLinMB) {
+		const bool vec = row_vec(w, K, dtype) && aligned16(x) && ldx % 4 == 0;
+		DISPATCH_DT(dtype, (linear_few_kernel<DT><<<dim3((N + 7) / 8, (M + kLinMB - 1) / kLinMB), 256, 0, st>>>(y, ldy, x, ldx, w, M, N, K, alpha, vec)));
+	} else {
+		DISPATCH_DT(dtype, (linear_tiled_kernel<DT><<<dim3((N + 63) / 64, (M + 63) / 64), 256, 0, st>>>(y, ldy, x, ldx, w, M, N, K, alpha)));
+	}
+	return (int)cudaGetLastError();
+}
+
+// out16 (M, K) = x (M, ldx) rounded to bf16 (bf16 != 0) or fp16
+extern "C" int yalm_cast_rows16(void *out16, const float *x, int ldx, int M, int K, int bf16, yalm_stream_t s) {
+	if (!out16 || !x || M < 1 || K < 1) return YALM_EINVAL;
+	if (bf16) cast_rows_kernel<__nv_bfloat16><<<M, 256, 0, (cudaStream_t)s>>>(static_cast<__nv_bfloat16 *>(out16), x, ldx, K);
+	else cast_rows_kernel<__half><<<M, 256, 0, (cudaStream_t)s>>>(static_cast<__half *>(out16), x, ldx, K);
+	return (int)cudaGetLastError();
+}
+
+// cache_f32 != 0: fp32 key / value ring, else bf16.
+extern "C" int yalm_qkv_post_rows(float *qkv, int ld, void *key_ring, void *value_ring, float *vfirst, int ldvf, const float *qnorm,
+                                  const float *knorm, const float *vmix, int vmode, int n, int n_heads, int n_kv, int dk, int dv, int ring,
+                                  float eps, int cache_f32, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!qkv || !key_ring || !value_ring || n < 1 || ring < 1 || (vmode && !vfirst) || (vmode == 2 && !vmix)) return YALM_EINVAL;
+	const int nq = n_heads * dk, nk = n_kv * dk, nv = n_kv * dv;
+	cudaStream_t st = (cudaStream_t)s;
+	if (cache_f32)
+		qkv_post_rows_kernel<float><<<n, 256, 0, st>>>(qkv, ld, (float *)key_ring, (float *)value_ring, vfirst, ldvf, qnorm, knorm, vmix, vmode, nq, nk,
+		                                               nv, dk, dv, ring, eps, pos0, ctl);
+	else
+		qkv_post_rows_kernel<__nv_bfloat16><<<n, 256, 0, st>>>(qkv, ld, (__nv_bfloat16 *)key_ring, (__nv_bfloat16 *)value_ring, vfirst, ldvf, qnorm,
+		                                                       knorm, vmix, vmode, nq, nk, nv, dk, dv, ring, eps, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_kv_pool_rows(float *key_pool, float *value_pool, const void *key_ring, const void *value_ring, int n, int n_kv, int dk, int dv,
+                                 int ring, int pool, int max_blocks, int cache_f32, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!key_pool || !value_pool || !key_ring || !value_ring || n < 1 || pool < 1 || max_blocks < 1) return YALM_EINVAL;
+	const dim3 grid(n / pool + 1, n_kv);
+	cudaStream_t st = (cudaStream_t)s;
+	if (cache_f32)
+		kv_pool_rows_kernel<float><<<grid, 128, 0, st>>>(key_pool, value_pool, (const float *)key_ring, (const float *)value_ring, n, dk, dv, ring, pool,
+		                                                 max_blocks, pos0, ctl);
+	else
+		kv_pool_rows_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(key_pool, value_pool, (const __nv_bfloat16 *)key_ring, (const __nv_bfloat16 *)value_ring,
+		                                                         n, dk, dv, ring, pool, max_blocks, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_attn_window_pool(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring, const float *key_pool,
+                                     const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks, int window,
+                                     int pool, float scale, int cache_f32, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!out || !q || !key_ring || !value_ring || n < 1 || n_kv < 1 || n_heads % n_kv || dv > 32 * kAttnMaxDvc || (pool > 0 && (!key_pool || !value_pool)))
+		return YALM_EINVAL;
+	const size_t smem = sizeof(float) * (((dk + 7) & ~7) + kAttnWarps * dv + kAttnWarps * 2);
+	if (smem > 48 * 1024) return YALM_EINVAL;
+	const dim3 grid(n_heads, n);
+	cudaStream_t st = (cudaStream_t)s;
+	if (cache_f32)
+		attn_window_pool_kernel<float><<<grid, kAttnWarps * 32, smem, st>>>(out, ldo, q, ldq, (const float *)key_ring, (const float *)value_ring, key_pool,
+		                                                                    value_pool, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale, pos0, ctl);
+	else
+		attn_window_pool_kernel<__nv_bfloat16><<<grid, kAttnWarps * 32, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)key_ring,
+		                                                                            (const __nv_bfloat16 *)value_ring, key_pool, value_pool, n_heads, n_kv, dk,
+		                                                                            dv, ring, max_blocks, window, pool, scale, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_norm_residual_rows(float *x, const float *y, int ldy, int nsum, const float *w, float w_offset, float eps, int n, int dim,
+                                       yalm_stream_t s) {
+	if (!x || !y || !w || n < 1 || nsum < 1 || dim < 1 || (size_t)dim * 4 > 48 * 1024) return YALM_EINVAL;
+	norm_residual_rows_kernel<<<n, 256, sizeof(float) * dim, (cudaStream_t)s>>>(x, y, ldy, nsum, w, w_offset, eps, dim);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, float w_offset, float eps, int n_rows, int dim,
+                                     yalm_stream_t s) {
+	if (!out || !x || !w || n_rows < 1) return YALM_EINVAL;
+	norm_gather_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)s>>>(out, x, rows, w, w_offset, eps, dim);
+	return (int)cudaGetLastError();
+}
+
+// act: YALM_ACT_GELU, YALM_ACT_SILU, or 2 = g * sigmoid(alpha g)
+extern "C" int yalm_glu_act_rows(float *h, const float *gu, int n, int ff, int act, float alpha, float limit, float up_offset, yalm_stream_t s) {
+	if (!h || !gu || n < 1 || ff < 1) return YALM_EINVAL;
+	glu_act_rows_kernel<<<dim3((ff + 255) / 256, n), 256, 0, (cudaStream_t)s>>>(h, gu, ff, act, alpha, limit, up_offset);
+	return (int)cudaGetLastError();
+}
+
+// score: 0 softmax, 1 sigmoid
+extern "C" int yalm_router_topk_rows(int *ids, float *wts, const float *x, int ldx, const void *wr, int dtype, int n, int n_experts, int top, int dim,
+                                     int score, int renorm, yalm_stream_t s) {
+	if (!ids || !wts || !x || !wr || n < 1 || top < 1 || top > n_experts || n_experts > 1024) return YALM_EINVAL;
+	const bool vec = row_vec(wr, dim, dtype) && aligned16(x) && ldx % 4 == 0;
+	DISPATCH_DT(dtype, (router_topk_rows_kernel<DT><<<n, 128, sizeof(float) * n_experts, (cudaStream_t)s>>>(ids, wts, x, ldx, wr, n_experts, top, dim,
+	                                                                                                      score, renorm, vec)));
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_moe_glu_slots(float *h, const float *x, int ldx, const void *wg, const void *wu, int dtype, const int *ids, const float *wts, int n,
+                                  int top, int ff, int dim, int act, float alpha, float limit, float up_offset, int in_scale, yalm_stream_t s) {
+	if (!h || !x || !wg || !wu || !ids || !wts || n < 1 || top < 1) return YALM_EINVAL;
+	const bool vec = row_vec(wg, dim, dtype) && row_vec(wu, dim, dtype) && aligned16(x) && ldx % 4 == 0;
+	DISPATCH_DT(dtype, (moe_glu_slots_kernel<DT><<<dim3((ff + 3) / 4, n * top), 128, 0, (cudaStream_t)s>>>(h, x, ldx, wg, wu, ids, wts, top, ff, dim, act,
+	                                                                                                     alpha, limit, up_offset, in_scale, vec)));
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_moe_down_slots(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top, int ff,
+                                   int dim, int out_scale, yalm_stream_t s) {
+	if (!y || !h || !wd || !ids || !wts || n < 1 || top < 1) return YALM_EINVAL;
+	const bool vec = row_vec(wd, ff, dtype) && aligned16(h) && ff % 4 == 0;
+	DISPATCH_DT(dtype, (moe_down_slots_kernel<DT><<<dim3((dim + 3) / 4, n * top), 128, 0, (cudaStream_t)s>>>(y, ldy, h, wd, ids, wts, ff, dim, out_scale, vec)));
+	return (int)cudaGetLastError();
+}

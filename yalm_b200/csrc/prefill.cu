@@ -263,6 +263,7 @@ struct Model::PrefillState {
 
 bool Model::supports_batch() const {
 	const Config &c = *config;
+	if (c.stack) return _device == Device::CUDA; // the layered executor takes any number of rows per call
 	const char *env = getenv("YALM_B200_PREFILL");
 	if (env && env[0] == '0') return false;
 	return _device == Device::CUDA && c.weight_dtype == DType::F16 && c.n_experts == 0 && c.tp_size == 1 &&
@@ -271,12 +272,17 @@ bool Model::supports_batch() const {
 }
 
 int Model::batch_capacity() const {
+	if (config->stack) return supports_batch() ? config->max_seq_len : 0;
 	return supports_batch() ? 512 : 0;
 }
 
 int Model::forward_batch(InferenceState &s, const int *tokens, int n, int pos0, const int *targets, float *probs_out) {
 	if (!supports_batch() || s.device() != Device::CUDA) return YALM_EINVAL;
 	const Config &c = *config;
+	if (c.stack) { // last row's logits for the samplers, or every row's probability of its target
+		const int last = n - 1;
+		return stack_rows(s, tokens, n, pos0, targets ? nullptr : &last, targets ? 0 : 1, nullptr, targets, probs_out);
+	}
 	const int cap = batch_capacity();
 	if (!tokens || n < 1 || n > cap || pos0 < 0 || pos0 + n > c.max_seq_len || (targets && !probs_out)) return YALM_EINVAL;
 	for (int i = 0; i < n; ++i)

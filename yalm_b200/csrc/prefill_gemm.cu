@@ -39,6 +39,8 @@ struct GemmArgs {
 	float *c;    // kStoreF32 / kAddF32: (M, ldc) fp32
 	__half *h;   // kGluF16: (M, ldc) fp16
 	int ldc;
+	float alpha; // kStoreF32 / kAddF32: the product is scaled before it is stored / added
+	int bf16;    // operands are bf16 instead of fp16 (same instruction kind, other format bits and tensor-map type)
 };
 
 // ---- PTX ---------------------------------------------------------------------------------------------------------
@@ -113,6 +115,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 __host__ __device__ constexpr uint32_t instr_desc_f16(int M, int N) {
 	return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// A format at [7,10) and B format at [10,13): 0 = fp16, 1 = bf16 (both operands the same type here)
+constexpr uint32_t kInstrDescBf16 = (1u << 7) | (1u << 10);
 
 // NB = 1: one W matrix, accumulator 128 x 128.  NB = 2: w1 | w3 tiles side by side, accumulator 128 x 256, GLU tail.
 template <int NB>
@@ -155,7 +159,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ 
 		}
 	} else if (warp == 1) {
 		if (lane == 0) { // ---- MMA issuer ----
-			constexpr uint32_t idesc = instr_desc_f16(BM, NACC);
+			const uint32_t idesc = instr_desc_f16(BM, NACC) | (g.bf16 ? kInstrDescBf16 : 0u);
 			for (int kb = 0; kb < nkb; ++kb) {
 				const int s = kb % kStages, r = kb / kStages;
 				mbar_wait(full0 + 8 * s, (uint32_t)r & 1u);
@@ -205,14 +209,14 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ 
 #pragma unroll
 					for (int i = 0; i < 32; i += 4) {
 						if (col + i + 4 <= g.N) {
-							float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+							float4 o = make_float4(g.alpha * v[i], g.alpha * v[i + 1], g.alpha * v[i + 2], g.alpha * v[i + 3]);
 							if (g.tail == kAddF32) { // x += W v (src/infer.cpp:335-337), residual stream stays fp32
 								const float4 x = *reinterpret_cast<const float4 *>(dst + i);
 								o.x += x.x, o.y += x.y, o.z += x.z, o.w += x.w;
 							}
 							*reinterpret_cast<float4 *>(dst + i) = o;
 						} else {
-							for (int j = i; j < i + 4 && col + j < g.N; ++j) dst[j] = g.tail == kAddF32 ? dst[j] + v[j] : v[j];
+							for (int j = i; j < i + 4 && col + j < g.N; ++j) dst[j] = g.tail == kAddF32 ? dst[j] + g.alpha * v[j] : g.alpha * v[j];
 						}
 					}
 				}
@@ -245,13 +249,13 @@ static EncodeTiledFn encode_fn() {
 }
 
 // (rows, cols) row-major fp16 matrix -> tensor map with a 128-row x 64-column box, 128-byte swizzle, zero fill past the edges
-static int make_map(CUtensorMap *map, const void *ptr, int rows, int cols) {
+static int make_map(CUtensorMap *map, const void *ptr, int rows, int cols, bool bf16 = false) {
 	EncodeTiledFn fn = encode_fn();
 	if (!fn) return YALM_EINVAL;
 	const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
 	const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
 	const cuuint32_t box[2] = {BK, BM}, estr[2] = {1, 1};
-	const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+	const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
 	                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
 	                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 	return r == CUDA_SUCCESS ? 0 : YALM_EINVAL;
@@ -278,14 +282,18 @@ using namespace yalm;
 using namespace yalm::prefill;
 
 // c (M, ldc) fp32 (=|+=) a (M, K) fp16 * w (N, K)^T fp16.  a, w, c: device pointers, 16-byte aligned rows (K % 8 == 0).
-extern "C" int yalm_gemm_f16(float *c, int ldc, const void *a, const void *w, int M, int N, int K, int accumulate, yalm_stream_t s) {
-	if (!c || !a || !w || M < 1 || N < 1 || K < 8 || K % 8 || ldc < N || ldc % 4) return YALM_EINVAL;
+extern "C" int yalm_gemm_16(float *c, int ldc, const void *a, const void *w, int M, int N, int K, int accumulate, int bf16, float alpha, yalm_stream_t s) {
+	if (!c || !a || !w || M < 1 || N < 1 || K < 8 || K % 8 || ldc < N || ldc % 4 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15))
+		return YALM_EINVAL;
 	CUtensorMap ta, tb;
-	int rc = make_map(&ta, a, M, K);
-	if (!rc) rc = make_map(&tb, w, N, K);
+	int rc = make_map(&ta, a, M, K, bf16 != 0);
+	if (!rc) rc = make_map(&tb, w, N, K, bf16 != 0);
 	if (rc) return rc;
-	GemmArgs g{M, N, K, accumulate ? kAddF32 : kStoreF32, 0, c, nullptr, ldc};
+	GemmArgs g{M, N, K, accumulate ? kAddF32 : kStoreF32, 0, c, nullptr, ldc, alpha, bf16 != 0};
 	return launch<1>(ta, tb, tb, g, (cudaStream_t)s);
+}
+extern "C" int yalm_gemm_f16(float *c, int ldc, const void *a, const void *w, int M, int N, int K, int accumulate, yalm_stream_t s) {
+	return yalm_gemm_16(c, ldc, a, w, M, N, K, accumulate, 0, 1.0f, s);
 }
 
 // h (M, ldh) fp16 = act(a w1^T) * (a w3^T): the fused w1 / w3 projection + GLU of the FFN (src/infer.cpp:360-375).
@@ -297,7 +305,7 @@ extern "C" int yalm_gemm_glu_f16(void *h, int ldh, const void *a, const void *w1
 	if (!rc) rc = make_map(&tb, w1, N, K);
 	if (!rc) rc = make_map(&tb2, w3, N, K);
 	if (rc) return rc;
-	GemmArgs g{M, N, K, kGluF16, act, nullptr, static_cast<__half *>(h), ldh};
+	GemmArgs g{M, N, K, kGluF16, act, nullptr, static_cast<__half *>(h), ldh, 1.0f, 0};
 	return launch<2>(ta, tb, tb2, g, (cudaStream_t)s);
 }
 

@@ -1,0 +1,547 @@
+// The layered executor: Model's path for architectures described by a StackSpec (arch.h) — a list of layers, each with
+// its own token mixer and feed-forward kind and sizes — where the reference has one homogeneous block (src/model.h:193-301).
+// It shares the rest of the library with the .yalm models: the checkpoint container and loader (one device arena, pinned
+// staging), InferenceState (stream, control block, logits, samplers), Model::forward / forward_batch / generate and the C
+// ABI above them.  One pass takes n consecutive positions; n = 1 is a decode step (token and position may come from the
+// device control block, so that sampling loops never leave the device), larger n is a portion of a prompt.
+//
+// Cache (owned by the model, like the reference's per-block key_cache / value_cache, src/model.h:238-240): per layer a
+// key ring and a value ring of `ring` slots (slot = position % ring; ring = window + chunk capacity for windowed layers
+// instead of the whole context, because a token that has left every window and whose block mean is taken is dead), plus,
+// for pooled layers, one fp32 mean key / value per completed block of tokens.  A sequence restarts at position 0 and may
+// only advance: the rings cannot seek.
+#include "arch.h"
+#include "loader.h"
+#include "yalm_api.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <iostream>
+
+#define ST_TRY(x)                                                                                                                  \
+	do {                                                                                                                           \
+		int rc__ = (int)(x);                                                                                                       \
+		if (rc__ != 0) return rc__;                                                                                                \
+	} while (0)
+
+namespace yalm {
+
+struct StackLayer {
+	LayerSpec spec;
+	// device
+	void *wqkv = nullptr, *wo = nullptr;     // (nq + nk + nv, dim), (dim, heads * vdim)
+	float *qnorm = nullptr, *knorm = nullptr, *vmix = nullptr, *norm1 = nullptr, *norm2 = nullptr;
+	void *wgu = nullptr, *wdown = nullptr;   // dense: (2 ff, dim) gate rows then up rows, (dim, ff)
+	void *wg = nullptr, *wu = nullptr;       // experts stacked: (E, ff, dim) each; wdown then is (E, dim, ff)
+	void *router = nullptr;                  // (E, dim)
+	void *kring = nullptr, *vring = nullptr; // (kv heads, ring, dim | vdim), fp32 or bf16
+	float *kpool = nullptr, *vpool = nullptr; // (kv heads, max_blocks, dim | vdim)
+	int ring = 0, max_blocks = 0;
+	int vmode = 0;                           // 0 plain values, 1 the first blending layer, 2 a later one
+};
+
+} // namespace yalm
+
+using yalm::FfnSpec;
+using yalm::LayerSpec;
+using yalm::StackLayer;
+using yalm::StackSpec;
+using yalm::TensorRole;
+
+// ------------------------------------------------------------------------------------------------------------------------
+// Config
+// ------------------------------------------------------------------------------------------------------------------------
+int Config::from_json(YALMData &data, int context, int compute) {
+	yalm::JValue j;
+	if (!yalm::json_parse(data.config_json.data(), data.config_json.size(), &j) || !j.is_object()) {
+		fprintf(stderr, "yalm_b200: config.json is not a JSON object\n");
+		return YALM_EFORMAT;
+	}
+	const std::string name = j["architecture"].string_or("");
+	const yalm::ArchEntry *a = yalm::find_arch(name);
+	if (!a) {
+		fprintf(stderr, "yalm_b200: unknown architecture '%s' (registered: %s)\n", name.c_str(), yalm::arch_names().c_str());
+		return YALM_EFORMAT;
+	}
+	const int rc = a->configure(j, *this);
+	if (rc) return rc;
+	const StackSpec &s = *stack;
+	const Tensor *emb = data.find(s.tensor_name(0, TensorRole::Embed, -1));
+	if (!emb) {
+		fprintf(stderr, "yalm_b200: the checkpoint has no embedding tensor\n");
+		return YALM_EFORMAT;
+	}
+	weight_dtype = compute >= 0 ? static_cast<DType>(compute) : emb->dtype;
+	if (weight_dtype != DType::F32 && weight_dtype != DType::F16 && weight_dtype != DType::BF16) {
+		fprintf(stderr, "yalm_b200: layered models compute in F32, F16 or BF16\n");
+		return YALM_EFORMAT;
+	}
+	// learned positions bound the context
+	if (context > 0) max_seq_len = s.learned_positions ? std::min(context, s.max_positions) : context;
+	if (const char *e = getenv("YALM_STACK_CHUNK")) stack_chunk = std::max(1, atoi(e));
+	return 0;
+}
+
+// ------------------------------------------------------------------------------------------------------------------------
+// Loading
+// ------------------------------------------------------------------------------------------------------------------------
+namespace {
+
+float widen(const void *p, size_t i, DType dt) {
+	if (dt == DType::F32) return static_cast<const float *>(p)[i];
+	const uint16_t u = static_cast<const uint16_t *>(p)[i];
+	if (dt == DType::BF16) {
+		const uint32_t w = (uint32_t)u << 16;
+		float f;
+		memcpy(&f, &w, 4);
+		return f;
+	}
+	// fp16
+	const uint32_t sign = (u >> 15) & 1, ex = (u >> 10) & 31, man = u & 1023;
+	uint32_t w;
+	if (ex == 0) {
+		if (man == 0) w = sign << 31;
+		else {
+			int e = -1;
+			uint32_t m = man;
+			do { ++e; m <<= 1; } while (!(m & 1024));
+			w = (sign << 31) | ((uint32_t)(127 - 15 - e) << 23) | ((m & 1023) << 13);
+		}
+	} else if (ex == 31) w = (sign << 31) | 0x7f800000u | (man << 13);
+	else w = (sign << 31) | ((ex + 112) << 23) | (man << 13);
+	float f;
+	memcpy(&f, &w, 4);
+	return f;
+}
+
+uint16_t narrow_bf16(float f) { // round to nearest even
+	uint32_t w;
+	memcpy(&w, &f, 4);
+	if ((w & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((w >> 16) | 0x40);
+	w += 0x7fffu + ((w >> 16) & 1);
+	return (uint16_t)(w >> 16);
+}
+
+[[noreturn]] void die(const std::string &msg) {
+	std::cerr << "FATAL: " << msg << std::endl;
+	abort();
+}
+
+} // namespace
+
+// Host bytes of tensor `t` in dtype `want` (the tensor's own bytes when it already is; else converted into a buffer the
+// model keeps until the upload).  Supported: anything -> F32, F32 -> BF16.
+static const void *host_as(std::vector<std::vector<char>> &keep, const Tensor *t, DType want, size_t numel) {
+	if (t->dtype == want) return t->data;
+	if (t->dtype != DType::F32 && t->dtype != DType::F16 && t->dtype != DType::BF16) die("tensor " + t->name + ": unsupported dtype " + dtype_to_string(t->dtype));
+	keep.emplace_back(numel * dtype_size(want));
+	char *dst = keep.back().data();
+	if (want == DType::F32) {
+		float *o = reinterpret_cast<float *>(dst);
+		for (size_t i = 0; i < numel; ++i) o[i] = widen(t->data, i, t->dtype);
+	} else if (want == DType::BF16) {
+		uint16_t *o = reinterpret_cast<uint16_t *>(dst);
+		for (size_t i = 0; i < numel; ++i) o[i] = narrow_bf16(widen(t->data, i, t->dtype));
+	} else
+		die("tensor " + t->name + ": no conversion " + dtype_to_string(t->dtype) + " -> " + dtype_to_string(want));
+	return dst;
+}
+
+namespace {
+// one device destination assembled from host parts laid one after the other
+struct Placement {
+	void **slot;
+	std::vector<std::pair<const void *, size_t>> parts;
+	size_t bytes() const {
+		size_t n = 0;
+		for (auto &p : parts) n += p.second;
+		return n;
+	}
+};
+} // namespace
+
+struct Model::StackScratch {
+	int cap = 0;
+	char *arena = nullptr;
+	float *x = nullptr, *qkv = nullptr, *vfirst = nullptr, *att = nullptr, *y = nullptr, *gu = nullptr, *h = nullptr, *wts = nullptr, *xn = nullptr,
+	      *logits = nullptr, *probs = nullptr;
+	void *a16 = nullptr;
+	int *ids = nullptr, *tokens = nullptr, *want = nullptr, *targets = nullptr;
+	std::vector<Placement> placements; // filled by build_stack, consumed by cuda_stack
+	~StackScratch() { cudaFree(arena); }
+};
+
+void Model::build_stack(YALMData &data) {
+	const Config &c = *config;
+	const StackSpec &s = *c.stack;
+	const DType dt = c.weight_dtype;
+	_scratch = std::make_shared<StackScratch>();
+	std::vector<Placement> &pl = _scratch->placements;
+	auto tensor = [&](int layer, TensorRole role, int expert, std::initializer_list<int> shape) -> const Tensor * {
+		const std::string name = s.tensor_name(layer, role, expert);
+		const Tensor *t = data.find(name);
+		if (!t) die("missing tensor: " + name);
+		size_t i = 0;
+		for (int d : shape) {
+			if (t->shape[i] != d) die("tensor " + name + ": unexpected shape");
+			++i;
+		}
+		for (; i < 4; ++i)
+			if (t->shape[i] != 0) die("tensor " + name + ": unexpected rank");
+		return t;
+	};
+	auto mat = [&](const Tensor *t) { return std::make_pair(host_as(_host_converted, t, dt, t->size / dtype_size(t->dtype)), t->size / dtype_size(t->dtype) * dtype_size(dt)); };
+	auto vec32 = [&](const Tensor *t) { return std::make_pair(host_as(_host_converted, t, DType::F32, t->size / dtype_size(t->dtype)), t->size / dtype_size(t->dtype) * 4); };
+
+	pl.push_back({&token_embedding_table, {mat(tensor(0, TensorRole::Embed, -1, {s.vocab, s.width}))}});
+	if (s.learned_positions) pl.push_back({&_pos_table, {mat(tensor(0, TensorRole::Positions, -1, {s.max_positions, s.width}))}});
+	pl.push_back({(void **)&rms_final_weight, {vec32(tensor(0, TensorRole::FinalNorm, -1, {s.width}))}});
+	pl.push_back({&wcls, {mat(tensor(0, TensorRole::Head, -1, {s.vocab, s.width}))}});
+	bool have_first = false;
+	for (int i = 0; i < (int)s.layers.size(); ++i) {
+		auto L = std::make_shared<StackLayer>();
+		L->spec = s.layers[i];
+		const yalm::MixerSpec &m = L->spec.mix;
+		const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, no = m.heads * m.vdim, W = s.width;
+		pl.push_back({&L->wqkv,
+		              {mat(tensor(i, TensorRole::Wq, -1, {nq, W})), mat(tensor(i, TensorRole::Wk, -1, {nk, W})), mat(tensor(i, TensorRole::Wv, -1, {nv, W}))}});
+		pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, no}))}});
+		if (m.qk_norm == yalm::QkNorm::WholeProjection) {
+			pl.push_back({(void **)&L->qnorm, {vec32(tensor(i, TensorRole::QNorm, -1, {nq}))}});
+			pl.push_back({(void **)&L->knorm, {vec32(tensor(i, TensorRole::KNorm, -1, {nk}))}});
+		}
+		if (m.v_mix) {
+			L->vmode = have_first ? 2 : 1;
+			have_first = true;
+			if (L->vmode == 2) pl.push_back({(void **)&L->vmix, {vec32(tensor(i, TensorRole::VMix, -1, {}))}});
+		}
+		pl.push_back({(void **)&L->norm1, {vec32(tensor(i, TensorRole::Norm1, -1, {W}))}});
+		const FfnSpec &f = L->spec.ffn;
+		if (f.kind != FfnSpec::None) pl.push_back({(void **)&L->norm2, {vec32(tensor(i, TensorRole::Norm2, -1, {W}))}});
+		if (f.kind == FfnSpec::Dense) {
+			pl.push_back({&L->wgu, {mat(tensor(i, TensorRole::Gate, -1, {f.ff, W})), mat(tensor(i, TensorRole::Up, -1, {f.ff, W}))}});
+			pl.push_back({&L->wdown, {mat(tensor(i, TensorRole::Down, -1, {W, f.ff}))}});
+		} else if (f.kind == FfnSpec::Moe) {
+			Placement g{&L->wg, {}}, u{&L->wu, {}}, d{&L->wdown, {}};
+			for (int e = 0; e < f.experts; ++e) {
+				g.parts.push_back(mat(tensor(i, TensorRole::Gate, e, {f.ff, W})));
+				u.parts.push_back(mat(tensor(i, TensorRole::Up, e, {f.ff, W})));
+				d.parts.push_back(mat(tensor(i, TensorRole::Down, e, {W, f.ff})));
+			}
+			pl.push_back(g), pl.push_back(u), pl.push_back(d);
+			pl.push_back({&L->router, {mat(tensor(i, TensorRole::Router, -1, {f.experts, W}))}});
+		}
+		// cache geometry
+		const int span = std::max(m.window, m.pool);
+		L->ring = m.window > 0 ? std::min(c.max_seq_len, (span + c.stack_chunk + 63) / 64 * 64) : c.max_seq_len;
+		L->max_blocks = m.pool > 0 ? c.max_seq_len / m.pool + 1 : 0;
+		_stack.push_back(L);
+	}
+	// v blending reads the first blending layer's values of the same rows: the shapes must agree
+	int first_nv = -1;
+	for (auto &L : _stack)
+		if (L->vmode) {
+			const int nv = L->spec.mix.kv_heads * L->spec.mix.vdim;
+			if (first_nv < 0) first_nv = nv;
+			else if (nv != first_nv) die("value blending needs the same number of value channels in every blending layer");
+		}
+}
+
+void Model::cuda_stack(int device) {
+	Config &c = *config;
+	const StackSpec &s = *c.stack;
+	c.tp_rank = 0, c.tp_size = 1;
+	_device = Device::CUDA;
+	set_cuda_device(device);
+	using yalm::DeviceArena;
+	const size_t cb = c.weight_dtype == DType::F32 ? 4 : 2; // cache element: fp32 in the 32-bit mode, bf16 otherwise
+	size_t need = 0;
+	for (const Placement &p : _scratch->placements) need += DeviceArena::padded(p.bytes());
+	for (auto &L : _stack) {
+		const yalm::MixerSpec &m = L->spec.mix;
+		need += DeviceArena::padded((size_t)m.kv_heads * L->ring * m.dim * cb) + DeviceArena::padded((size_t)m.kv_heads * L->ring * m.vdim * cb);
+		if (m.pool > 0)
+			need += DeviceArena::padded((size_t)m.kv_heads * L->max_blocks * m.dim * 4) + DeviceArena::padded((size_t)m.kv_heads * L->max_blocks * m.vdim * 4);
+	}
+	_arena = std::make_shared<DeviceArena>();
+	if (int rc = _arena->reserve(need)) die(std::string("device allocation failed: ") + cudaGetErrorString((cudaError_t)rc));
+	yalm::Uploader up;
+	for (const Placement &p : _scratch->placements) {
+		char *dst = static_cast<char *>(_arena->take(p.bytes()));
+		if (!dst) die("device arena exhausted (loader sizing bug)");
+		*p.slot = dst;
+		for (auto &part : p.parts) {
+			if (up.put(dst, part.first, part.second, 0, part.second, 1)) die("upload failed");
+			dst += part.second;
+			_device_bytes += part.second;
+		}
+	}
+	for (auto &L : _stack) {
+		const yalm::MixerSpec &m = L->spec.mix;
+		const size_t kb = (size_t)m.kv_heads * L->ring * m.dim * cb, vb = (size_t)m.kv_heads * L->ring * m.vdim * cb;
+		L->kring = _arena->take(kb), L->vring = _arena->take(vb);
+		if (!L->kring || !L->vring) die("device arena exhausted (cache)");
+		up.zero(L->kring, kb), up.zero(L->vring, vb);
+		_device_bytes += kb + vb;
+		if (m.pool > 0) {
+			const size_t pk = (size_t)m.kv_heads * L->max_blocks * m.dim * 4, pv = (size_t)m.kv_heads * L->max_blocks * m.vdim * 4;
+			L->kpool = static_cast<float *>(_arena->take(pk)), L->vpool = static_cast<float *>(_arena->take(pv));
+			if (!L->kpool || !L->vpool) die("device arena exhausted (pooled cache)");
+			up.zero(L->kpool, pk), up.zero(L->vpool, pv);
+			_device_bytes += pk + pv;
+		}
+	}
+	if (up.finish()) die("upload failed");
+	_upload_pinned = up.pinned();
+	_scratch->placements.clear();
+	_host_converted.clear();
+	_host_converted.shrink_to_fit();
+	// per-pass scratch for stack_chunk rows
+	StackScratch &S = *_scratch;
+	S.cap = c.stack_chunk;
+	const size_t cap = S.cap, W = s.width, top = std::max(1, s.max_top()), ff = std::max(1, s.max_ff());
+	const size_t nqkv = (size_t)s.max_q_dim() + s.max_kv_dim() + s.max_v_dim();
+	const size_t kmax = std::max({W, (size_t)s.max_o_dim(), ff});
+	auto pad = [](size_t b) { return (b + 255) / 256 * 256; };
+	struct Slot {
+		void **p;
+		size_t bytes;
+	} slots[] = {{(void **)&S.x, 4 * cap * W},           {(void **)&S.qkv, 4 * cap * nqkv},      {(void **)&S.vfirst, 4 * cap * std::max<size_t>(1, s.max_v_dim())},
+	             {(void **)&S.att, 4 * cap * std::max<size_t>(1, s.max_o_dim())},                   {(void **)&S.y, 4 * cap * top * W},
+	             {(void **)&S.gu, 4 * cap * 2 * ff},     {(void **)&S.h, 4 * cap * top * ff},    {(void **)&S.wts, 4 * cap * top},
+	             {(void **)&S.xn, 4 * cap * W},          {(void **)&S.logits, 4 * cap * (size_t)s.vocab}, {(void **)&S.probs, 4 * cap},
+	             {(void **)&S.a16, 2 * cap * top * kmax}, {(void **)&S.ids, 4 * cap * top},       {(void **)&S.tokens, 4 * cap},
+	             {(void **)&S.want, 4 * cap},            {(void **)&S.targets, 4 * cap}};
+	size_t total = 0;
+	for (auto &sl : slots) total += pad(sl.bytes);
+	if (cudaMalloc((void **)&S.arena, total) != cudaSuccess) die("device allocation failed (pass scratch)");
+	cudaMemset(S.arena, 0, total);
+	char *p = S.arena;
+	for (auto &sl : slots) *sl.p = p, p += pad(sl.bytes);
+	if (cudaDeviceSynchronize() != cudaSuccess) die("device error after upload");
+}
+
+// ------------------------------------------------------------------------------------------------------------------------
+// One pass: n rows whose tokens are in scratch.tokens (or in the control block), positions pos0 .. (or ctl)
+// ------------------------------------------------------------------------------------------------------------------------
+// y = alpha * x W^T.  16-bit weights and enough rows: activations rounded once to the weight type, product on the tcgen05
+// tensor cores (prefill_gemm.cu); otherwise (fp32 mode, few rows, rows that are not 16-byte multiples) the SIMT routes,
+// which keep the activations in fp32.
+static int stack_linear(Model &, const Config &c, void *a16, float *y, int ldy, const float *x, int ldx, const void *w, int M, int N, int K,
+                        float alpha, cudaStream_t st) {
+	const int dt = static_cast<int>(c.weight_dtype);
+	static const bool tc_off = [] { const char *e = getenv("YALM_STACK_TC"); return e && e[0] == '0'; }();
+	if (!tc_off && dt != YALM_F32 && M >= 32 && K % 8 == 0 && K >= 8 && ldy % 4 == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+		ST_TRY(yalm_cast_rows16(a16, x, ldx, M, K, dt == YALM_BF16, st));
+		return yalm_gemm_16(y, ldy, a16, w, M, N, K, 0, dt == YALM_BF16, alpha, st);
+	}
+	return yalm_linear_rows(y, ldy, x, ldx, w, dt, M, N, K, alpha, st);
+}
+
+int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want) {
+	const Config &c = *config;
+	const StackSpec &sp = *c.stack;
+	StackScratch &S = *_scratch;
+	cudaStream_t st = s.stream();
+	const int dt = static_cast<int>(c.weight_dtype), W = sp.width, f32 = c.weight_dtype == DType::F32;
+	const int *ctl = from_ctl ? s.ctl() : nullptr;
+	const float woff = sp.norm_one_plus ? 1.f : 0.f;
+	ST_TRY(yalm_embed_rows(S.x, token_embedding_table, _pos_table, dt, from_ctl ? nullptr : S.tokens, n, W, pos0, ctl, st));
+	for (auto &Lp : _stack) {
+		const StackLayer &L = *Lp;
+		const yalm::MixerSpec &m = L.spec.mix;
+		const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, no = m.heads * m.vdim, ld = nq + nk + nv;
+		// ---- token mixer ----
+		ST_TRY(stack_linear(*this, c, S.a16, S.qkv, ld, S.x, W, L.wqkv, n, ld, W, 1.f, st));
+		ST_TRY(yalm_qkv_post_rows(S.qkv, ld, L.kring, L.vring, S.vfirst, nv, L.qnorm, L.knorm, L.vmix, L.vmode, n, m.heads, m.kv_heads, m.dim, m.vdim,
+		                          L.ring, sp.norm_eps, f32, pos0, ctl, st));
+		if (m.pool > 0)
+			ST_TRY(yalm_kv_pool_rows(L.kpool, L.vpool, L.kring, L.vring, n, m.kv_heads, m.dim, m.vdim, L.ring, m.pool, L.max_blocks, f32, pos0, ctl, st));
+		ST_TRY(yalm_attn_window_pool(S.att, no, S.qkv, ld, L.kring, L.vring, L.kpool, L.vpool, n, m.heads, m.kv_heads, m.dim, m.vdim, L.ring,
+		                             L.max_blocks, m.window, m.pool, m.scale, f32, pos0, ctl, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.y, W, S.att, no, L.wo, n, W, no, 1.f, st));
+		ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, 1, L.norm1, woff, sp.norm_eps, n, W, st));
+		// ---- feed-forward ----
+		const FfnSpec &f = L.spec.ffn;
+		const int act = f.act == yalm::GluAct::SigmoidScaled ? 2 : f.act == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
+		if (f.kind == FfnSpec::Dense) {
+			ST_TRY(stack_linear(*this, c, S.a16, S.gu, 2 * f.ff, S.x, W, L.wgu, n, 2 * f.ff, W, 1.f, st));
+			ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.ff, act, f.act_alpha, f.limit, f.up_offset, st));
+			ST_TRY(stack_linear(*this, c, S.a16, S.y, W, S.h, f.ff, L.wdown, n, W, f.ff, 1.f, st));
+			ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, 1, L.norm2, woff, sp.norm_eps, n, W, st));
+		} else if (f.kind == FfnSpec::Moe) {
+			ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.x, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
+			                             f.renormalize ? 1 : 0, st));
+			ST_TRY(yalm_moe_glu_slots(S.h, S.x, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
+			                          f.weight_on_input ? 1 : 0, st));
+			ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
+			ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, f.top, L.norm2, woff, sp.norm_eps, n, W, st));
+		}
+	}
+	if (n_want > 0) {
+		ST_TRY(yalm_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, woff, sp.norm_eps, n_want, W, st));
+		// a single wanted row lands directly where the samplers read it
+		float *dst = n_want == 1 ? s.logits_dev() : S.logits;
+		ST_TRY(stack_linear(*this, c, S.a16, dst, sp.vocab, S.xn, W, wcls, n_want, sp.vocab, W, sp.logit_scale, st));
+	}
+	return (int)cudaGetLastError();
+}
+
+int Model::stack_rows(InferenceState &s, const int *tokens, int n, int pos0, const int *want, int n_want, float *logits_out, const int *targets,
+                      float *probs_out) {
+	if (_device != Device::CUDA || s.device() != Device::CUDA) return YALM_ENOGPU;
+	const Config &c = *config;
+	const int V = c.vocab_size;
+	if (!tokens || n < 1 || pos0 < 0 || pos0 + n > c.max_seq_len || n_want < 0 || (n_want && !want) || (targets && !probs_out)) return YALM_EINVAL;
+	if (pos0 != 0 && pos0 != _stack_pos) {
+		fprintf(stderr, "yalm_b200: position %d does not continue the sequence (next is %d; 0 starts a new one)\n", pos0, _stack_pos);
+		return YALM_EINVAL;
+	}
+	for (int i = 0; i < n; ++i)
+		if (tokens[i] < 0 || tokens[i] >= V) return YALM_EINVAL;
+	for (int i = 0; i < n_want; ++i)
+		if (want[i] < 0 || want[i] >= n || (i && want[i] <= want[i - 1])) return YALM_EINVAL;
+	StackScratch &S = *_scratch;
+	cudaStream_t st = s.stream();
+	std::vector<int> all;
+	if (targets) { // every row's logits, for the probability of its target
+		all.resize(n);
+		for (int i = 0; i < n; ++i) all[i] = i;
+		want = all.data(), n_want = n;
+	}
+	int wi = 0;
+	bool have_last = false;
+	for (int done = 0; done < n; done += S.cap) {
+		const int m = std::min(S.cap, n - done);
+		int w0 = wi;
+		while (wi < n_want && want[wi] < done + m) ++wi;
+		const int nw = wi - w0;
+		std::vector<int> local(std::max(1, nw));
+		for (int i = 0; i < nw; ++i) local[i] = want[w0 + i] - done;
+		ST_TRY(cudaMemcpyAsync(S.tokens, tokens + done, sizeof(int) * m, cudaMemcpyHostToDevice, st));
+		if (nw) ST_TRY(cudaMemcpyAsync(S.want, local.data(), sizeof(int) * nw, cudaMemcpyHostToDevice, st));
+		if (targets) ST_TRY(cudaMemcpyAsync(S.targets, targets + done, sizeof(int) * m, cudaMemcpyHostToDevice, st));
+		ST_TRY(stack_pass(s, m, pos0 + done, false, nw));
+		if (nw) {
+			const float *src = nw == 1 ? s.logits_dev() : S.logits;
+			if (nw > 1) // the last wanted row stays where the samplers read it
+				ST_TRY(cudaMemcpyAsync(s.logits_dev(), S.logits + (size_t)(nw - 1) * V, sizeof(float) * V, cudaMemcpyDeviceToDevice, st));
+			if (logits_out && !targets) ST_TRY(cudaMemcpyAsync(logits_out + (size_t)w0 * V, src, sizeof(float) * nw * V, cudaMemcpyDeviceToHost, st));
+			if (targets) {
+				ST_TRY(yalm_token_probs(src, V, nw, S.targets, S.probs, st));
+				ST_TRY(cudaMemcpyAsync(probs_out + done, S.probs, sizeof(float) * nw, cudaMemcpyDeviceToHost, st));
+			}
+			have_last = true;
+		}
+		ST_TRY(cudaStreamSynchronize(st)); // `local` and the caller's arrays are host memory
+	}
+	_stack_pos = pos0 + n;
+	if (have_last && s.host_logits()) {
+		ST_TRY(cudaMemcpyAsync(s.logits(), s.logits_dev(), sizeof(float) * V, cudaMemcpyDeviceToHost, st));
+		ST_TRY(cudaStreamSynchronize(st));
+	}
+	return (int)cudaGetLastError();
+}
+
+int Model::forward_rows(InferenceState &s, const int *tokens, int n, int pos0, const int *want, int n_want, float *logits_out) {
+	if (is_stack()) return stack_rows(s, tokens, n, pos0, want, n_want, logits_out, nullptr, nullptr);
+	// .yalm models: the token loop (src/main.cpp:91-97), logits kept for the wanted rows
+	if (_device != Device::CUDA || s.device() != Device::CUDA) return YALM_ENOGPU;
+	if (!tokens || n < 1 || pos0 < 0 || (n_want && (!want || !logits_out))) return YALM_EINVAL;
+	const bool host = s.host_logits();
+	s.set_host_logits(true);
+	int wi = 0;
+	for (int i = 0; i < n; ++i) {
+		if (tokens[i] < 0 || tokens[i] >= config->vocab_size) return YALM_EINVAL;
+		const bool wanted = wi < n_want && want[wi] == i;
+		forward(s, tokens[i], pos0 + i, wanted ? InferenceMode::OUTPUT_LOGITS : InferenceMode::HYDRATE_KV_CACHE);
+		if (wanted) memcpy(logits_out + (size_t)wi++ * config->vocab_size, s.logits(), sizeof(float) * config->vocab_size);
+	}
+	s.set_host_logits(host);
+	return 0;
+}
+
+void Model::end_sequence(InferenceState &) {
+	_stack_pos = 0; // rings and pooled blocks are overwritten from position 0 on; nothing of the old sequence is read again
+}
+
+// Decode loop on the device: token and position live in the control block, the sampler advances them, and only the token ids
+// come back.  After one eager step the step (all kernels of a pass + the sampler) is replayed as one CUDA graph.
+int Model::stack_generate(InferenceState &s, int token, int pos, int n_gen, float temperature, unsigned long long seed, int *tokens_out,
+                          float *logits_out, float *device_ms) {
+	if (_device != Device::CUDA || s.device() != Device::CUDA) return YALM_ENOGPU;
+	const Config &c = *config;
+	if (n_gen < 1 || n_gen > s.tokens_capacity() || token < 0 || token >= c.vocab_size || pos < 0 || pos + n_gen > c.max_seq_len || !tokens_out ||
+	    !(temperature >= 0.f) || (pos != 0 && pos != _stack_pos))
+		return YALM_EINVAL;
+	cudaStream_t st = s.stream();
+	int h[YALM_CTL_INTS] = {token, pos, 0, pos % c.max_seq_len, std::min(pos + 1, c.max_seq_len), 0, 0, 0};
+	ST_TRY(cudaMemcpyAsync(s.ctl(), h, sizeof(h), cudaMemcpyHostToDevice, st));
+	ST_TRY(cudaStreamSynchronize(st));
+	cudaEvent_t e0, e1;
+	ST_TRY(cudaEventCreate(&e0));
+	ST_TRY(cudaEventCreate(&e1));
+	const bool greedy = temperature == 0.f;
+	auto step = [&]() -> int {
+		ST_TRY(stack_pass(s, 1, 0, true, 1));
+		if (greedy) return yalm_argmax_advance(s.logits_dev(), c.vocab_size, s.ctl(), c.max_seq_len, s.tokens_dev(), st);
+		return yalm_sample_advance(s.logits_dev(), c.vocab_size, s.ctl(), c.max_seq_len, s.tokens_dev(), temperature, seed, st);
+	};
+	// one graph per sampling mode would need the temperature and seed baked in: capture the greedy step only
+	CudaGraph &g = s.greedy_graph(); // per inference state: the graph holds the state's control block and logits pointers
+	const bool use_graph = greedy && !logits_out;
+	ST_TRY(cudaEventRecord(e0, st));
+	for (int i = 0; i < n_gen; ++i) {
+		if (use_graph && g.is_created) g.launch(st);
+		else {
+			ST_TRY(step());
+			if (logits_out)
+				ST_TRY(cudaMemcpyAsync(logits_out + (size_t)i * c.vocab_size, s.logits_dev(), sizeof(float) * c.vocab_size, cudaMemcpyDeviceToHost, st));
+			if (use_graph) {
+				ST_TRY(cudaStreamSynchronize(st));
+				ST_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+				const int rc = step();
+				const cudaError_t end = cudaStreamEndCapture(st, &g.graph);
+				if (rc || end != cudaSuccess) return rc ? rc : (int)end;
+				ST_TRY(cudaGraphInstantiate(&g.instance, g.graph, 0));
+				g.is_created = true;
+			}
+		}
+	}
+	ST_TRY(cudaEventRecord(e1, st));
+	ST_TRY(cudaMemcpyAsync(tokens_out, s.tokens_dev(), sizeof(int) * n_gen, cudaMemcpyDeviceToHost, st));
+	ST_TRY(cudaStreamSynchronize(st));
+	if (device_ms) ST_TRY(cudaEventElapsedTime(device_ms, e0, e1));
+	cudaEventDestroy(e0), cudaEventDestroy(e1);
+	_stack_pos = pos + n_gen;
+	return (int)cudaGetLastError();
+}
+
+int Model::stack_ring_slots(int layer) const {
+	return layer >= 0 && layer < (int)_stack.size() ? _stack[layer]->ring : -1;
+}
+
+int Model::stack_read(int layer, int which, float *dst, size_t count) {
+	if (layer < 0 || layer >= (int)_stack.size() || !dst || which < 0 || which > 3) return YALM_EINVAL;
+	const StackLayer &L = *_stack[layer];
+	const yalm::MixerSpec &m = L.spec.mix;
+	ST_TRY(cudaDeviceSynchronize());
+	if (which >= 2) {
+		if (!L.kpool) return YALM_EINVAL;
+		const size_t n = (size_t)m.kv_heads * L.max_blocks * (which == 2 ? m.dim : m.vdim);
+		if (count > n) return YALM_EINVAL;
+		return (int)cudaMemcpy(dst, which == 2 ? L.kpool : L.vpool, count * 4, cudaMemcpyDeviceToHost);
+	}
+	const size_t n = (size_t)m.kv_heads * L.ring * (which == 0 ? m.dim : m.vdim);
+	if (count > n) return YALM_EINVAL;
+	const void *src = which == 0 ? L.kring : L.vring;
+	if (config->weight_dtype == DType::F32) return (int)cudaMemcpy(dst, src, count * 4, cudaMemcpyDeviceToHost);
+	std::vector<uint16_t> tmp(count);
+	ST_TRY(cudaMemcpy(tmp.data(), src, count * 2, cudaMemcpyDeviceToHost));
+	for (size_t i = 0; i < count; ++i) dst[i] = widen(tmp.data(), i, DType::BF16);
+	return 0;
+}

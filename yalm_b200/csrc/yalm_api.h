@@ -21,6 +21,8 @@
 namespace yalm {
 class DeviceArena;
 class Uploader;
+struct StackSpec;  // arch.h: a layered architecture's list of layers with their mechanisms and sizes
+struct StackLayer; // stack.cpp: one such layer's weights and caches on the device
 } // namespace yalm
 
 constexpr int KV_SINKS = 2; // src/model.h:12
@@ -49,9 +51,20 @@ struct Config {
 	// expert parallelism for the MoE FFN (net-new, the measured alternative of SURVEY.md 8(e)): rank r holds whole experts
 	// e with e % tp_size == r instead of a 1 / tp_size slice of every expert; attention and the LM head stay tensor-parallel
 	bool moe_ep = false;
+	// Layered architectures (checkpoint directories whose config.json names a registered architecture, arch.h): every
+	// layer has its own sizes, so the fields above only summarise (dim, vocab_size, n_layers, max_seq_len are exact, the
+	// rest are maxima for scratch sizing) and `stack` holds the description the layered executor runs.  Null for .yalm models.
+	std::shared_ptr<yalm::StackSpec> stack;
+	// Layered executor: most rows (consecutive positions) one pass takes; longer inputs are walked in pieces of this size.
+	// It also sizes the key / value rings of windowed layers (window + stack_chunk slots instead of max_seq_len).
+	int stack_chunk = 512;
 
 	// If nonzero `context` is supplied, max sequence length is set to `context` (src/model.cpp:31-36).
 	void from_yalm(YALMData &yalm, int context = 0);
+	// config.json of a checkpoint directory -> the registered architecture's reader.  `compute`: the dtype the weights are
+	// held and multiplied in (F32: true 32-bit everywhere; F16 / BF16: 16-bit operands, fp32 accumulation); negative: as stored.
+	// Returns 0 or YALM_EFORMAT.
+	int from_json(YALMData &data, int context, int compute);
 	// Exact weight + KV bytes one token reads at position `pos`; unlike the
 	// reference's (src/model.cpp:77-102) the LM head is counted at its real element size.
 	size_t active_bytes(size_t pos) const;
@@ -235,7 +248,8 @@ struct Model {
 	void *wcls = nullptr;                  // (vocab_size / tp, dim)
 	float *wcls_scale = nullptr;
 
-	explicit Model(YALMData &yalm, int context = 0);
+	// compute_dtype: layered architectures only (Config::from_json); .yalm models run in the dtype they are stored in.
+	explicit Model(YALMData &yalm, int context = 0, int compute_dtype = -1);
 	~Model();
 	Model(const Model &) = delete;
 
@@ -266,6 +280,18 @@ struct Model {
 	bool supports_batch() const;
 	int batch_capacity() const;
 	int forward_batch(InferenceState &s, const int *tokens, int n, int pos0, const int *targets, float *probs_out);
+	// The general step: n consecutive positions pos0 .. pos0 + n - 1 of the current sequence (n = 1: a decode step; larger:
+	// a portion of a prompt, cut anywhere), from the cache earlier steps left.  want[0 .. n_want) are row indices (ascending)
+	// whose logits are copied to logits_out (host, n_want x vocab).  The last wanted row's logits also stay in
+	// s.logits_dev() / logits() for the samplers.  Layered models run it natively (any n); .yalm models walk the rows with
+	// forward().  Returns 0 or an error code.
+	int forward_rows(InferenceState &s, const int *tokens, int n, int pos0, const int *want, int n_want, float *logits_out);
+	// The current sequence is finished: its cache is given back and the next step must start at position 0.
+	void end_sequence(InferenceState &s);
+	bool is_stack() const { return config->stack != nullptr; }
+	// layered models: per-layer taps for tests (which: 0 key ring, 1 value ring, 2 pooled keys, 3 pooled values -> fp32 copies)
+	int stack_read(int layer, int which, float *dst, size_t count);
+	int stack_ring_slots(int layer) const;
 	size_t device_bytes() const { return _device_bytes; }
 	// loader facts for tests / bench: number of device allocations behind the model (1) and whether the upload went through pinned staging
 	int device_allocations() const { return _arena ? 1 : 0; }
@@ -291,6 +317,21 @@ private:
 	std::shared_ptr<MegaState> _mega;
 	struct PrefillState; // chunk workspace of forward_batch (prefill.cu), created on first use
 	std::shared_ptr<PrefillState> _prefill;
+	// ---- layered executor (stack.cpp) ----
+	friend struct yalm::StackLayer;
+	std::vector<std::shared_ptr<yalm::StackLayer>> _stack;
+	void *_pos_table = nullptr;                     // learned positions (max_positions, dim), weight dtype
+	std::vector<std::vector<char>> _host_converted; // weights converted on the host (bf16 -> fp32, norm weights), alive until the upload
+	struct StackScratch;
+	std::shared_ptr<StackScratch> _scratch;
+	int _stack_pos = 0; // next position of the current sequence
+	void build_stack(YALMData &data);
+	void cuda_stack(int device);
+	int stack_rows(InferenceState &s, const int *tokens, int n, int pos0, const int *want, int n_want, float *logits_out, const int *targets,
+	               float *probs_out);
+	int stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want);
+	int stack_generate(InferenceState &s, int token, int pos, int n_gen, float temperature, unsigned long long seed, int *tokens_out,
+	                   float *logits_out, float *device_ms);
 	Device _device = Device::CPU;
 	bool _tied = false;
 	std::shared_ptr<yalm::DeviceArena> _arena; // ONE device allocation: every weight shard + every KV cache of this rank
