@@ -230,6 +230,11 @@ int yalm_token_probs_host(const float *logits, int vocab, int n_rows, const int 
 /* Host-pointer test entry of the prefill GEMM: c (M, N) fp32 = a (M, K) fp16 * w (N, K)^T fp16 [+ c if accumulate];
  * with w3 != NULL instead h (M, N) fp16 = act(a w^T) * (a w3^T). */
 int yalm_gemm_host(float *c, void *h, const void *a, const void *w, const void *w3, int M, int N, int K, int accumulate, int act);
+/* Host-pointer test entry of the windowed attention with pooled blocks: positions 0 .. T - 1 in portions of `chunk` rows
+ * through the append, block-mean and attention kernels over rings of `ring` slots (>= max(window, pool) + chunk - 1).
+ * q (T, n_heads dk), k (T, n_kv dk), v (T, n_kv dv), out (T, n_heads dv), fp32. */
+int yalm_attn_window_pool_host(float *out, const float *q, const float *k, const float *v, int T, int n_heads, int n_kv, int dk, int dv,
+                               int window, int pool, float scale, int ring, int chunk, int cache_f32);
 /* Same ops timed on the device: `iters` launches after `warmup`, returns mean microseconds per
  * launch (CUDA events) in *usec.  This is what `./build/test -k <name>` prints. */
 int yalm_bench_op(const char *name, int iters, int warmup, double *usec, double *bytes);

@@ -36,7 +36,7 @@ SYMBOLS = [
     "yalm_model_batch_capacity", "yalm_forward_batch", "yalm_generate", "yalm_state_debug_set_launch_seq", "yalm_tokenize", "yalm_detokenize",
     "yalm_embed_rows", "yalm_linear_rows", "yalm_cast_rows16", "yalm_gemm_16", "yalm_qkv_post_rows", "yalm_kv_pool_rows", "yalm_attn_window_pool",
     "yalm_norm_residual_rows", "yalm_norm_gather_rows", "yalm_glu_act_rows", "yalm_router_topk_rows", "yalm_moe_glu_slots", "yalm_moe_down_slots",
-    "yalm_model_open_dir", "yalm_model_is_stack", "yalm_forward_rows", "yalm_sequence_end", "yalm_stack_read", "yalm_stack_ring_slots",
+    "yalm_model_open_dir", "yalm_model_is_stack", "yalm_forward_rows", "yalm_sequence_end", "yalm_stack_read", "yalm_stack_ring_slots", "yalm_attn_window_pool_host",
     "yalm_tp_unique_id", "yalm_tp_init", "yalm_tp_finalize", "yalm_tp_shard_plan", "yalm_mega_tile_plan", "yalm_mega_attn_split", "yalm_mega_mma_plan", "yalm_mega_hb_share", "yalm_error_string", "yalm_version",
 ]
 
@@ -74,6 +74,7 @@ def lib():
     L.yalm_sequence_end.argtypes = [vp, vp]
     L.yalm_stack_read.argtypes = [vp, i, i, vp, sz]
     L.yalm_stack_ring_slots.argtypes = [vp, i]
+    L.yalm_attn_window_pool_host.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, i, i]
     L.yalm_model_cuda.argtypes = [vp, i, i, i]
     L.yalm_model_close.argtypes = [vp]
     L.yalm_model_close.restype = None
@@ -214,6 +215,17 @@ def detokenize(image, ids) -> bytes:
     if n < 0:
         raise YalmError(n, "detokenize")
     return buf.raw[:n]
+
+
+def attn_window_pool(q, k, v, n_heads, n_kv, window, pool, scale, ring, chunk, cache_f32=True):
+    """Windowed attention with pooled blocks over positions 0 .. T - 1, walked in portions of `chunk` rows over rings of
+    `ring` slots.  q (T, n_heads, dk), k (T, n_kv, dk), v (T, n_kv, dv) -> (T, n_heads, dv)."""
+    T, dk, dv = q.shape[0], q.shape[2], v.shape[2]
+    q, k, v = (np.ascontiguousarray(a, np.float32) for a in (q, k, v))
+    out = np.zeros((T, n_heads, dv), np.float32)
+    _check(lib().yalm_attn_window_pool_host(_p(out), _p(q), _p(k), _p(v), T, n_heads, n_kv, dk, dv, window, pool, scale, ring, chunk,
+                                            1 if cache_f32 else 0), "attn_window_pool")
+    return out
 
 
 def bench_op(name: str, iters: int = 20, warmup: int = 3):

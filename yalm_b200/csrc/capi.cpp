@@ -256,6 +256,43 @@ extern "C" int yalm_bench_op(const char *name, int iters, int warmup, double *us
 	return 0;
 }
 
+// Host-pointer test entry of the windowed attention with pooled blocks: positions 0 .. T - 1 walked in portions of
+// `chunk` rows through the product's own append (yalm_qkv_post_rows without norms), block-mean (yalm_kv_pool_rows) and
+// attention kernels over rings of `ring` slots.  q (T, H dk), k (T, G dk), v (T, G dv), out (T, H dv), all fp32.
+extern "C" int yalm_attn_window_pool_host(float *out, const float *q, const float *k, const float *v, int T, int n_heads, int n_kv, int dk, int dv,
+                                          int window, int pool, float scale, int ring, int chunk, int cache_f32) {
+	if (!have_gpu()) return YALM_ENOGPU;
+	if (!out || !q || !k || !v || T < 1 || chunk < 1 || ring < std::max(window, pool) + chunk - 1 || n_kv < 1 || n_heads % n_kv) return YALM_EINVAL;
+	const int nq = n_heads * dk, nk = n_kv * dk, nv = n_kv * dv, ld = nq + nk + nv, no = n_heads * dv;
+	const int max_blocks = pool > 0 ? T / pool + 1 : 1;
+	const size_t cb = cache_f32 ? 4 : 2;
+	std::vector<float> rows((size_t)T * ld);
+	for (int t = 0; t < T; ++t) {
+		memcpy(&rows[(size_t)t * ld], q + (size_t)t * nq, sizeof(float) * nq);
+		memcpy(&rows[(size_t)t * ld + nq], k + (size_t)t * nk, sizeof(float) * nk);
+		memcpy(&rows[(size_t)t * ld + nq + nk], v + (size_t)t * nv, sizeof(float) * nv);
+	}
+	DevBuf dqkv(rows.data(), sizeof(float) * rows.size()), dkr, dvr, dkp, dvp, dout;
+	RET_IF(dkr.alloc((size_t)n_kv * ring * dk * cb));
+	RET_IF(dvr.alloc((size_t)n_kv * ring * dv * cb));
+	RET_IF(dkp.alloc(sizeof(float) * n_kv * max_blocks * dk));
+	RET_IF(dvp.alloc(sizeof(float) * n_kv * max_blocks * dv));
+	RET_IF(dout.alloc(sizeof(float) * (size_t)T * no));
+	for (int p0 = 0; p0 < T; p0 += chunk) {
+		const int n = std::min(chunk, T - p0);
+		float *r = dqkv.as<float>() + (size_t)p0 * ld;
+		RET_IF(yalm_qkv_post_rows(r, ld, dkr.p, dvr.p, nullptr, 0, nullptr, nullptr, nullptr, 0, n, n_heads, n_kv, dk, dv, ring, 0.f, cache_f32, p0,
+		                          nullptr, nullptr));
+		if (pool > 0)
+			RET_IF(yalm_kv_pool_rows(dkp.as<float>(), dvp.as<float>(), dkr.p, dvr.p, n, n_kv, dk, dv, ring, pool, max_blocks, cache_f32, p0, nullptr, nullptr));
+		RET_IF(yalm_attn_window_pool(dout.as<float>() + (size_t)p0 * no, no, r, ld, dkr.p, dvr.p, pool > 0 ? dkp.as<float>() : nullptr,
+		                             pool > 0 ? dvp.as<float>() : nullptr, n, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale, cache_f32, p0,
+		                             nullptr, nullptr));
+	}
+	RET_IF(cudaDeviceSynchronize());
+	return (int)cudaMemcpy(out, dout.p, sizeof(float) * (size_t)T * no, cudaMemcpyDeviceToHost);
+}
+
 // ---- (3b) opaque handles --------------------------------------------------------------------------------
 struct yalm_model {
 	YALMData data;
