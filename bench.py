@@ -45,6 +45,8 @@ WORKLOADS = {
     "llama-3.2-1b-fp32": ("llama-3.2-1b", "fp32", 4096, "Llama-3.2-1B fp32 random-init, batch-1 decode"),
     "tiny": ("tiny-moe", "fp16", 64, "tiny MoE test model (debug only)"),
     # batched prefill: a different metric (prompt tokens hydrated per second), its own line
+    # the layered design at model-like sizes beside the equal-size .yalm block (yalm_b200/stack_bench.py): prefill and decode, one line
+    "retezen-sizes": ("tiny", "bf16", 4096, "Retezen (windowed attention with pooled blocks, dense / routed feed-forward) at model-like sizes"),
     "mistral-7b-fp16-prefill": ("mistral-7b", "fp16", 4096, "Mistral-7B-v0.2 fp16 random-init, 4096-token prompt hydrated in 512-token chunks (tcgen05 GEMMs)"),
 }
 HEADLINE = "mistral-7b-fp16-4k"
@@ -355,6 +357,11 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; yalm_b200 has no CPU fallback (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local_rank)
+    if args.workload == "retezen-sizes":
+        if world > 1:
+            raise SystemExit("bench.py: the layered models run on one GPU")
+        from yalm_b200 import stack_bench
+        return stack_bench.run(args, base, _emit, write_model, shm_path, ClockSampler)
     if args.workload.endswith("-prefill"):
         if world > 1:
             raise SystemExit("bench.py: the prefill workload is single-GPU")

@@ -158,6 +158,9 @@ int yalm_token_probs(const float *logits, int vocab, int n_rows, const int *targ
 int yalm_gemv(float *xout, const float *x, const void *w, const float *scale, int n, int d, int dtype,
               yalm_stream_t s);
 
+/* xout = alpha * W x; also takes YALM_BF16 weights (n % 8 == 0, 16-byte aligned rows). */
+int yalm_gemv_scaled(float *xout, const float *x, const void *w, int n, int d, int dtype, float alpha, yalm_stream_t s);
+
 /* ---- (2b) batched prefill ops (net-new, SURVEY.md 8(f).1: the reference hydrates and scores token by token,
  * src/main.cpp:91-97, 174-184) ---------------------------------------------------------------------------------------
  * c (M, ldc) fp32 (=|+=) a (M, K) fp16 * w (N, K)^T fp16 on the tcgen05 tensor cores (TMA operand loads, TMEM
@@ -194,10 +197,21 @@ int yalm_qkv_post_rows(float *qkv, int ld, void *key_ring, void *value_ring, flo
 int yalm_kv_pool_rows(float *key_pool, float *value_pool, const void *key_ring, const void *value_ring, int n, int n_kv, int dk, int dv,
                       int ring, int pool, int max_blocks, int cache_f32, int pos0, const int *ctl, yalm_stream_t s);
 /* Attention of n query rows: position i sees tokens j with 0 <= i - j < window (window 0: all) and, if pool > 0, block b
- * (positions b pool .. b pool + pool - 1) once b pool + pool - 1 <= i - window; one softmax over both; score = q . k * scale. */
+ * (positions b pool .. b pool + pool - 1) once b pool + pool - 1 <= i - window; one softmax over both; score = q . k * scale.
+ * The key / value rows are read once for up to four query heads that share a kv head.  workspace (optional,
+ * yalm_attn_window_pool_workspace(dv) floats): with few rows (decoding) the keys are split over more CTAs and merged in order;
+ * context: the most positions a sequence reaches (0: unknown), used to pick the split count from shapes alone. */
+size_t yalm_attn_window_pool_workspace(int dv);
 int yalm_attn_window_pool(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring,
-                          const float *key_pool, const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring,
-                          int max_blocks, int window, int pool, float scale, int cache_f32, int pos0, const int *ctl, yalm_stream_t s);
+                          const float *key_pool, const float *value_pool, float *workspace, int n, int n_heads, int n_kv, int dk, int dv,
+                          int ring, int max_blocks, int window, int pool, float scale, int cache_f32, int context, int pos0, const int *ctl,
+                          yalm_stream_t s);
+/* The same attention for many rows over bf16 rings on the tensor cores (mma.sync bf16, fp32 scores / softmax): head sizes
+ * dk in {64, 128}, dv in {32, 64, 128} (yalm_attn_window_pool_mma_shape), ldq % 4 == 0, ldo % 2 == 0. */
+int yalm_attn_window_pool_mma_shape(int dk, int dv);
+int yalm_attn_window_pool_mma(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring,
+                              const float *key_pool, const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring,
+                              int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, yalm_stream_t s);
 /* x[m] += rms(sum_{j < nsum} y[m * nsum + j]) * (w_offset + w) */
 int yalm_norm_residual_rows(float *x, const float *y, int ldy, int nsum, const float *w, float w_offset, float eps, int n, int dim,
                             yalm_stream_t s);

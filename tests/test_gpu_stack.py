@@ -123,6 +123,19 @@ def test_attention_bf16_cache_means_are_taken_over_the_cached_values():
     close_enough(got, want, 2e-5)
 
 
+@pytest.mark.parametrize("dk,dv,H,G,window,pool,chunk", [
+    (64, 32, 4, 2, 40, 8, 64), (128, 128, 2, 1, 40, 8, 23), (64, 128, 3, 3, 100, 16, 200), (128, 64, 4, 1, 7, 3, 64),
+    (64, 64, 2, 2, 0, 0, 70), (128, 32, 2, 1, 150, 1, 64), (64, 32, 4, 4, 33, 64, 16), (128, 128, 4, 2, 64, 64, 128)])
+def test_attention_on_the_tensor_cores(dk, dv, H, G, window, pool, chunk):
+    # portions of 16 rows and more over bf16 rings take the mma route; same crafted peaks at every edge
+    T = 200
+    q, k, v = crafted_qkv(T, H, G, dk, dv, window, pool, seed=dk + dv + window)
+    want = O.window_pool_attention(O.round_bf16(q), k, v, window, pool, 0.2, cache_round=O.round_bf16)
+    span = max(window, pool) if window > 0 else T
+    got = api.attn_window_pool(q, k, v, H, G, window, pool, 0.2, span + chunk - 1 if window > 0 else T, chunk, cache_f32=False)
+    close_enough(got, want, 1.5e-2)       # the weights are rounded to bf16 as the operand of P V
+
+
 # ---- mechanisms through small models ---------------------------------------------------------------------------------
 @pytest.mark.parametrize("name,layers", [
     ("attention only", [O.attn_layer(mlp=None, v_mix=False)]),

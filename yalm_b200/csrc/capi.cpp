@@ -278,6 +278,8 @@ extern "C" int yalm_attn_window_pool_host(float *out, const float *q, const floa
 	RET_IF(dkp.alloc(sizeof(float) * n_kv * max_blocks * dk));
 	RET_IF(dvp.alloc(sizeof(float) * n_kv * max_blocks * dv));
 	RET_IF(dout.alloc(sizeof(float) * (size_t)T * no));
+	DevBuf dws;
+	RET_IF(dws.alloc(sizeof(float) * yalm_attn_window_pool_workspace(dv)));
 	for (int p0 = 0; p0 < T; p0 += chunk) {
 		const int n = std::min(chunk, T - p0);
 		float *r = dqkv.as<float>() + (size_t)p0 * ld;
@@ -285,9 +287,14 @@ extern "C" int yalm_attn_window_pool_host(float *out, const float *q, const floa
 		                          nullptr, nullptr));
 		if (pool > 0)
 			RET_IF(yalm_kv_pool_rows(dkp.as<float>(), dvp.as<float>(), dkr.p, dvr.p, n, n_kv, dk, dv, ring, pool, max_blocks, cache_f32, p0, nullptr, nullptr));
+		if (!cache_f32 && n >= 16 && ld % 4 == 0 && no % 2 == 0 && yalm_attn_window_pool_mma_shape(dk, dv))
+			RET_IF(yalm_attn_window_pool_mma(dout.as<float>() + (size_t)p0 * no, no, r, ld, dkr.p, dvr.p, pool > 0 ? dkp.as<float>() : nullptr,
+			                                 pool > 0 ? dvp.as<float>() : nullptr, n, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale, p0, nullptr,
+			                                 nullptr));
+		else
 		RET_IF(yalm_attn_window_pool(dout.as<float>() + (size_t)p0 * no, no, r, ld, dkr.p, dvr.p, pool > 0 ? dkp.as<float>() : nullptr,
-		                             pool > 0 ? dvp.as<float>() : nullptr, n, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale, cache_f32, p0,
-		                             nullptr, nullptr));
+		                             pool > 0 ? dvp.as<float>() : nullptr, dws.as<float>(), n, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale,
+		                             cache_f32, T, p0, nullptr, nullptr));
 	}
 	RET_IF(cudaDeviceSynchronize());
 	return (int)cudaMemcpy(out, dout.p, sizeof(float) * (size_t)T * no, cudaMemcpyDeviceToHost);

@@ -134,6 +134,29 @@ struct WTraits<YALM_F16> {
 	}
 };
 
+// bf16: the upper half of an fp32, so widening is a shift / mask (layered models; the .yalm kernels are not instantiated for it)
+template <>
+struct WTraits<YALM_BF16> {
+	static constexpr int EP = 8;
+	static constexpr int BYTES = 2;
+	__device__ static __forceinline__ float lo(uint32_t u) { return __uint_as_float(u << 16); }
+	__device__ static __forceinline__ float hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+	__device__ static __forceinline__ float fma16(uint4 w, const float4 *xv, float acc) {
+		acc = fmaf(lo(w.x), xv[0].x, acc);
+		acc = fmaf(hi(w.x), xv[0].y, acc);
+		acc = fmaf(lo(w.y), xv[0].z, acc);
+		acc = fmaf(hi(w.y), xv[0].w, acc);
+		acc = fmaf(lo(w.z), xv[1].x, acc);
+		acc = fmaf(hi(w.z), xv[1].y, acc);
+		acc = fmaf(lo(w.w), xv[1].z, acc);
+		acc = fmaf(hi(w.w), xv[1].w, acc);
+		return acc;
+	}
+	__device__ static __forceinline__ float to_float(const void *p, size_t i) {
+		return __uint_as_float((uint32_t) static_cast<const uint16_t *>(p)[i] << 16);
+	}
+};
+
 template <>
 struct WTraits<YALM_F8E4M3> {
 	static constexpr int EP = 16;

@@ -288,6 +288,7 @@ struct RowsArgs {
 	const float *scale;
 	int n, d;
 	float eps;
+	float alpha; // the product is scaled by it (1: the plain GEMV)
 };
 
 template <int DT, int R, int U>
@@ -312,7 +313,7 @@ __global__ void __launch_bounds__(kThreads) gemv_rows_kernel(RowsArgs a) {
 #pragma unroll
 		for (int r = 0; r < R; ++r)
 			if (lane == r && row + r < a.d)
-				a.out[row + r] = (DT == YALM_F8E4M3 && a.scale) ? acc[r] * a.scale[row + r] : acc[r];
+				a.out[row + r] = a.alpha * ((DT == YALM_F8E4M3 && a.scale) ? acc[r] * a.scale[row + r] : acc[r]);
 	}
 }
 
@@ -368,7 +369,7 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float *__res
 using namespace yalm;
 
 static inline int ep_of(int dtype) {
-	return dtype == YALM_F32 ? 4 : dtype == YALM_F16 ? 8 : dtype == YALM_F8E4M3 ? 16 : 0;
+	return dtype == YALM_F32 ? 4 : (dtype == YALM_F16 || dtype == YALM_BF16) ? 8 : dtype == YALM_F8E4M3 ? 16 : 0;
 }
 static inline size_t xs_bytes(int dtype, int n) {
 	const int ch = 32 * ep_of(dtype);
@@ -477,14 +478,21 @@ extern "C" int yalm_ffn_glu_ep(float *hb, const float *x, const float *rms_weigh
 }
 
 static int rows_launch(float *out, const float *x, const float *rms_w, const void *w, const float *scale, int n,
-                       int d, float eps, int dtype, cudaStream_t st) {
+                       int d, float eps, int dtype, cudaStream_t st, float alpha = 1.f) {
 	const int ep = ep_of(dtype);
 	if (!ep || !out || !x || !w || n <= 0 || d <= 0 || n % ep) return YALM_EINVAL;
 	RowsArgs a;
-	a.out = out, a.x = x, a.rms_w = rms_w, a.w = (const char *)w, a.scale = scale, a.n = n, a.d = d, a.eps = eps;
+	a.out = out, a.x = x, a.rms_w = rms_w, a.w = (const char *)w, a.scale = scale, a.n = n, a.d = d, a.eps = eps, a.alpha = alpha;
 	const size_t smem = 36 * sizeof(float) + xs_bytes(dtype, n);
+	if (dtype == YALM_BF16) // bf16 weights exist for this kernel only (the layered models' one-row products)
+		return launch_persistent(gemv_rows_kernel<YALM_BF16, 4, 4>, a, smem, (d + 3) / 4, st);
 	YALM_DISPATCH_DT(dtype, return launch_persistent(gemv_rows_kernel<DT, 4, 4>, a, smem, (d + 3) / 4, st));
 	return 0;
+}
+
+// xout = alpha * W x, weights fp32 / fp16 / bf16 / fp8: the bare GEMV with a scale (the layered models' one-row products)
+extern "C" int yalm_gemv_scaled(float *xout, const float *x, const void *w, int n, int d, int dtype, float alpha, yalm_stream_t s) {
+	return rows_launch(xout, x, nullptr, w, nullptr, n, d, 0.f, dtype, (cudaStream_t)s, alpha);
 }
 
 extern "C" int yalm_lm_head(float *logits, const float *x, const float *rms_weight, const void *wcls,

@@ -21,6 +21,8 @@
 
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
 #include "gemv.cuh"
 
 namespace yalm {
@@ -79,14 +81,24 @@ __device__ __forceinline__ float warp_dot(const void *w, size_t row_off, const f
 	float acc = 0.f;
 	if (vec) {
 		const typename E::T *row = static_cast<const typename E::T *>(w) + row_off;
-		for (int k = lane * E::VEC; k < K; k += 32 * E::VEC) {
-			float f[8];
-			E::unpack(ldg_stream(row + k), f);
+		constexpr int U = 4, STEP = 32 * E::VEC; // U loads in flight per lane before the first multiply
+		for (int k0 = lane * E::VEC; k0 < K; k0 += U * STEP) {
+			uint4 wv[U];
 #pragma unroll
-			for (int i = 0; i < E::VEC; i += 4) {
-				const float4 xv = *reinterpret_cast<const float4 *>(x + k + i);
-				acc = fmaf(f[i], xv.x, acc), acc = fmaf(f[i + 1], xv.y, acc), acc = fmaf(f[i + 2], xv.z, acc), acc = fmaf(f[i + 3], xv.w, acc);
-			}
+			for (int u = 0; u < U; ++u)
+				if (k0 + u * STEP < K) wv[u] = ldg_stream(row + k0 + u * STEP);
+#pragma unroll
+			for (int u = 0; u < U; ++u)
+				if (k0 + u * STEP < K) {
+					float f[8];
+					E::unpack(wv[u], f);
+					const int k = k0 + u * STEP;
+#pragma unroll
+					for (int i = 0; i < E::VEC; i += 4) {
+						const float4 xv = *reinterpret_cast<const float4 *>(x + k + i);
+						acc = fmaf(f[i], xv.x, acc), acc = fmaf(f[i + 1], xv.y, acc), acc = fmaf(f[i + 2], xv.z, acc), acc = fmaf(f[i + 3], xv.w, acc);
+					}
+				}
 		}
 	} else {
 		for (int k = lane; k < K; k += 32) acc = fmaf(E::get(w, row_off + k), x[k], acc);
@@ -284,114 +296,186 @@ __global__ void kv_pool_rows_kernel(float *__restrict__ kp, float *__restrict__ 
 // ---- attention: sliding window + pooled blocks, one softmax ------------------------------------------------------------
 // Query row m at position i = p0 + m sees the tokens lo .. i (lo = max(0, i - window + 1); window 0: lo = 0) and, when
 // pool > 0, the blocks 0 .. nb - 1 with nb = floor((i - window + 1) / pool): those whose last token has left the window.
-// One CTA per (head, row); its warps take 32-key tiles in turn: lane = key for the scores (each lane walks its own key
-// row), online softmax per warp in fp32, then lane = value channel for P V.  Warps merge in shared memory.
+// One CTA per (kv head x group of up to R query heads that share it, row, split): the key / value rows are read once for
+// the R heads.  Its warps take 32-key tiles in turn: lane = key for the scores (each lane walks its own key row against
+// the R queries in shared memory), online softmax per warp and head in fp32, then lane = value channel for P V.  Warps
+// merge in shared memory; with more than one split (few rows: decoding) the CTA leaves an unnormalised partial
+// (accumulator, max, sum) and attn_merge_kernel combines the splits in order.
 constexpr int kAttnWarps = 4;
-constexpr int kAttnMaxDvc = 8; // value channels per lane: vdim <= 256
+constexpr int kAttnMaxParts = 4096; // (row, head, split) partials the workspace holds
 
-template <typename CT>
-__device__ __forceinline__ float key_dot(const CT *krow, const float *qs, int dk, bool vec);
-template <>
-__device__ __forceinline__ float key_dot<float>(const float *krow, const float *qs, int dk, bool vec) {
-	float s = 0.f;
+template <typename CT, int R>
+__device__ __forceinline__ void key_dots(const CT *krow, const float *qs, int dkp, int dk, bool vec, float (&s)[R]);
+template <int R>
+__device__ __forceinline__ void key_dots_f32(const float *krow, const float *qs, int dkp, int dk, bool vec, float (&s)[R]) {
 	if (vec) {
 		for (int d = 0; d < dk; d += 4) {
-			const float4 kv = *reinterpret_cast<const float4 *>(krow + d), qv = *reinterpret_cast<const float4 *>(qs + d);
-			s = fmaf(kv.x, qv.x, s), s = fmaf(kv.y, qv.y, s), s = fmaf(kv.z, qv.z, s), s = fmaf(kv.w, qv.w, s);
+			const float4 kv = *reinterpret_cast<const float4 *>(krow + d);
+#pragma unroll
+			for (int r = 0; r < R; ++r) {
+				const float4 qv = *reinterpret_cast<const float4 *>(qs + r * dkp + d);
+				s[r] = fmaf(kv.x, qv.x, s[r]), s[r] = fmaf(kv.y, qv.y, s[r]), s[r] = fmaf(kv.z, qv.z, s[r]), s[r] = fmaf(kv.w, qv.w, s[r]);
+			}
 		}
 	} else
-		for (int d = 0; d < dk; ++d) s = fmaf(krow[d], qs[d], s);
-	return s;
+		for (int d = 0; d < dk; ++d) {
+			const float kv = krow[d];
+#pragma unroll
+			for (int r = 0; r < R; ++r) s[r] = fmaf(kv, qs[r * dkp + d], s[r]);
+		}
 }
-template <>
-__device__ __forceinline__ float key_dot<__nv_bfloat16>(const __nv_bfloat16 *krow, const float *qs, int dk, bool vec) {
-	float s = 0.f;
+template <int R>
+__device__ __forceinline__ void key_dots_bf16(const __nv_bfloat16 *krow, const float *qs, int dkp, int dk, bool vec, float (&s)[R]) {
 	if (vec) {
 		for (int d = 0; d < dk; d += 8) {
 			float f[8];
 			Elem<YALM_BF16>::unpack(*reinterpret_cast<const uint4 *>(krow + d), f);
 #pragma unroll
-			for (int i = 0; i < 8; ++i) s = fmaf(f[i], qs[d + i], s);
+			for (int r = 0; r < R; ++r) {
+				const float4 q0 = *reinterpret_cast<const float4 *>(qs + r * dkp + d), q1 = *reinterpret_cast<const float4 *>(qs + r * dkp + d + 4);
+				s[r] = fmaf(f[0], q0.x, s[r]), s[r] = fmaf(f[1], q0.y, s[r]), s[r] = fmaf(f[2], q0.z, s[r]), s[r] = fmaf(f[3], q0.w, s[r]);
+				s[r] = fmaf(f[4], q1.x, s[r]), s[r] = fmaf(f[5], q1.y, s[r]), s[r] = fmaf(f[6], q1.z, s[r]), s[r] = fmaf(f[7], q1.w, s[r]);
+			}
 		}
 	} else
-		for (int d = 0; d < dk; ++d) s = fmaf(cache_get(krow, d), qs[d], s);
-	return s;
+		for (int d = 0; d < dk; ++d) {
+			const float kv = cache_get(krow, d);
+#pragma unroll
+			for (int r = 0; r < R; ++r) s[r] = fmaf(kv, qs[r * dkp + d], s[r]);
+		}
+}
+template <int R> __device__ __forceinline__ void key_dots_any(const float *krow, const float *qs, int dkp, int dk, bool vec, float (&s)[R]) {
+	key_dots_f32<R>(krow, qs, dkp, dk, vec, s);
+}
+template <int R> __device__ __forceinline__ void key_dots_any(const __nv_bfloat16 *krow, const float *qs, int dkp, int dk, bool vec, float (&s)[R]) {
+	key_dots_bf16<R>(krow, qs, dkp, dk, vec, s);
 }
 
-template <typename CT>
+template <typename CT, int R, int DVC>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
                                                                            const CT *__restrict__ kc, const CT *__restrict__ vc,
-                                                                           const float *__restrict__ kp, const float *__restrict__ vp, int n_heads,
-                                                                           int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool,
-                                                                           float scale, int pos0, const int *__restrict__ ctl) {
+                                                                           const float *__restrict__ kp, const float *__restrict__ vp,
+                                                                           float *__restrict__ part, int n_heads, int n_kv, int dk, int dv, int ring,
+                                                                           int max_blocks, int window, int pool, float scale, int pos0,
+                                                                           const int *__restrict__ ctl) {
 	extern __shared__ __align__(16) float sm[];
-	float *qs = sm;                              // dk (padded to 8)
-	float *macc = sm + ((dk + 7) & ~7);          // kAttnWarps x dv
-	float *mml = macc + kAttnWarps * dv;         // kAttnWarps x 2
-	const int h = blockIdx.x, m = blockIdx.y, g = h / (n_heads / n_kv);
+	const int dkp = (dk + 7) & ~7;
+	float *qs = sm;                                    // R x dkp
+	float *macc = qs + R * dkp;                        // kAttnWarps x R x dv
+	float *mml = macc + kAttnWarps * R * dv;           // kAttnWarps x R x 2
+	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
+	const int g = blockIdx.x / hg, h0 = g * rep + (blockIdx.x % hg) * R, nh = min(R, g * rep + rep - h0);
+	const int m = blockIdx.y, z = blockIdx.z, nsplit = gridDim.z;
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int i = first_pos(ctl, pos0) + m;
 	const int lo = window > 0 ? max(0, i - window + 1) : 0;
 	const int nb = (window > 0 && pool > 0 && i - window + 1 >= pool) ? (i - window + 1) / pool : 0;
 	const int nkeys = nb + (i - lo + 1);
-	for (int d = threadIdx.x; d < dk; d += blockDim.x) qs[d] = q[(size_t)m * ldq + (size_t)h * dk + d] * scale;
+	for (int e = threadIdx.x; e < R * dkp; e += blockDim.x) {
+		const int r = e / dkp, d = e % dkp;
+		qs[e] = (r < nh && d < dk) ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
+	}
 	__syncthreads();
 	const CT *kbase = kc + (size_t)g * ring * dk, *vbase = vc + (size_t)g * ring * dv;
 	const float *kpb = kp ? kp + (size_t)g * max_blocks * dk : nullptr, *vpb = vp ? vp + (size_t)g * max_blocks * dv : nullptr;
 	const bool kvec_c = (dk * sizeof(CT)) % 16 == 0 && aligned16(kbase), kvec_p = (dk * 4) % 16 == 0 && aligned16(kpb);
-	float mx = -INFINITY, l = 0.f, acc[kAttnMaxDvc];
+	float mx[R], l[R], acc[R][DVC];
 #pragma unroll
-	for (int c = 0; c < kAttnMaxDvc; ++c) acc[c] = 0.f;
-	for (int t0 = warp * 32; t0 < nkeys; t0 += kAttnWarps * 32) {
-		const int u = t0 + lane;
-		float s = -INFINITY;
+	for (int r = 0; r < R; ++r) {
+		mx[r] = -INFINITY, l[r] = 0.f;
+#pragma unroll
+		for (int c = 0; c < DVC; ++c) acc[r][c] = 0.f;
+	}
+	const int ntiles = (nkeys + 31) / 32, per = (ntiles + nsplit - 1) / nsplit;
+	const int t_end = min(ntiles, (z + 1) * per);
+	for (int t = z * per + warp; t < t_end; t += kAttnWarps) {
+		const int t0 = t * 32, u = t0 + lane;
+		float s[R], p[R];
+#pragma unroll
+		for (int r = 0; r < R; ++r) s[r] = 0.f;
 		if (u < nkeys) {
-			if (u < nb) s = key_dot<float>(kpb + (size_t)u * dk, qs, dk, kvec_p);
-			else s = key_dot<CT>(kbase + (size_t)((lo + u - nb) % ring) * dk, qs, dk, kvec_c);
+			if (u < nb) key_dots_f32<R>(kpb + (size_t)u * dk, qs, dkp, dk, kvec_p, s);
+			else key_dots_any<R>(kbase + (size_t)((lo + u - nb) % ring) * dk, qs, dkp, dk, kvec_c, s);
 		}
-		const float tmax = warp_max(s);              // finite: the tile holds at least one key
-		const float nmx = fmaxf(mx, tmax);
-		const float corr = mx == -INFINITY ? 0.f : expf(mx - nmx);
-		const float p = u < nkeys ? expf(s - nmx) : 0.f;
-		l = l * corr + warp_sum(p);
-		mx = nmx;
 #pragma unroll
-		for (int c = 0; c < kAttnMaxDvc; ++c) acc[c] *= corr;
+		for (int r = 0; r < R; ++r) {
+			const float sv = u < nkeys ? s[r] : -INFINITY;
+			const float nmx = fmaxf(mx[r], warp_max(sv));     // finite: the tile holds at least one key
+			const float corr = mx[r] == -INFINITY ? 0.f : expf(mx[r] - nmx);
+			p[r] = u < nkeys ? expf(sv - nmx) : 0.f;
+			l[r] = l[r] * corr + warp_sum(p[r]);
+			mx[r] = nmx;
+#pragma unroll
+			for (int c = 0; c < DVC; ++c) acc[r][c] *= corr;
+		}
 		const int cnt = min(32, nkeys - t0);
 		for (int kk = 0; kk < cnt; ++kk) {
-			const float pk = __shfl_sync(kFull, p, kk);
 			const int uk = t0 + kk;
+			float vv[DVC];
 			if (uk < nb) {
 				const float *vr = vpb + (size_t)uk * dv;
 #pragma unroll
-				for (int c = 0; c < kAttnMaxDvc; ++c)
-					if (c * 32 + lane < dv) acc[c] = fmaf(pk, vr[c * 32 + lane], acc[c]);
+				for (int c = 0; c < DVC; ++c) vv[c] = c * 32 + lane < dv ? vr[c * 32 + lane] : 0.f;
 			} else {
 				const CT *vr = vbase + (size_t)((lo + uk - nb) % ring) * dv;
 #pragma unroll
-				for (int c = 0; c < kAttnMaxDvc; ++c)
-					if (c * 32 + lane < dv) acc[c] = fmaf(pk, cache_get(vr, c * 32 + lane), acc[c]);
+				for (int c = 0; c < DVC; ++c) vv[c] = c * 32 + lane < dv ? cache_get(vr, c * 32 + lane) : 0.f;
+			}
+#pragma unroll
+			for (int r = 0; r < R; ++r) {
+				const float pk = __shfl_sync(kFull, p[r], kk);
+#pragma unroll
+				for (int c = 0; c < DVC; ++c) acc[r][c] = fmaf(pk, vv[c], acc[r][c]);
 			}
 		}
 	}
 #pragma unroll
-	for (int c = 0; c < kAttnMaxDvc; ++c)
-		if (c * 32 + lane < dv) macc[warp * dv + c * 32 + lane] = acc[c];
-	if (lane == 0) mml[warp * 2] = mx, mml[warp * 2 + 1] = l;
+	for (int r = 0; r < R; ++r) {
+#pragma unroll
+		for (int c = 0; c < DVC; ++c)
+			if (c * 32 + lane < dv) macc[(warp * R + r) * dv + c * 32 + lane] = acc[r][c];
+		if (lane == 0) mml[(warp * R + r) * 2] = mx[r], mml[(warp * R + r) * 2 + 1] = l[r];
+	}
 	__syncthreads();
-	if (warp == 0) {
+	for (int r = warp; r < nh; r += kAttnWarps) { // one warp finishes one head
 		float M = -INFINITY;
-		for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, mml[w * 2]);
+		for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, mml[(w * R + r) * 2]);
 		float wt[kAttnWarps], L = 0.f;
 		for (int w = 0; w < kAttnWarps; ++w) {
-			wt[w] = mml[w * 2] == -INFINITY ? 0.f : expf(mml[w * 2] - M);
-			L += wt[w] * mml[w * 2 + 1];
+			const float mw = mml[(w * R + r) * 2];
+			wt[w] = mw == -INFINITY ? 0.f : expf(mw - M);
+			L += wt[w] * mml[(w * R + r) * 2 + 1];
 		}
+		const int h = h0 + r;
+		float *pr = part ? part + ((size_t)(m * n_heads + h) * nsplit + z) * (dv + 2) : nullptr;
 		for (int c = lane; c < dv; c += 32) {
 			float o = 0.f;
-			for (int w = 0; w < kAttnWarps; ++w) o += wt[w] * macc[w * dv + c];
-			out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+			for (int w = 0; w < kAttnWarps; ++w) o += wt[w] * macc[(w * R + r) * dv + c];
+			if (pr) pr[c] = o;
+			else out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
 		}
+		if (pr && lane == 0) pr[dv] = M, pr[dv + 1] = L;
+	}
+}
+
+// out[m, h, :] = sum_z w_z acc_z / sum_z w_z L_z with w_z = exp(M_z - max M), splits taken in order.  grid (heads, rows).
+__global__ void attn_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit) {
+	const int h = blockIdx.x, m = blockIdx.y;
+	const float *pr = part + (size_t)(m * n_heads + h) * nsplit * (dv + 2);
+	float M = -INFINITY;
+	for (int z = 0; z < nsplit; ++z) M = fmaxf(M, pr[(size_t)z * (dv + 2) + dv]);
+	float L = 0.f;
+	for (int z = 0; z < nsplit; ++z) {
+		const float mz = pr[(size_t)z * (dv + 2) + dv];
+		if (mz != -INFINITY) L += expf(mz - M) * pr[(size_t)z * (dv + 2) + dv + 1];
+	}
+	for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+		float o = 0.f;
+		for (int z = 0; z < nsplit; ++z) {
+			const float mz = pr[(size_t)z * (dv + 2) + dv];
+			if (mz != -INFINITY) o += expf(mz - M) * pr[(size_t)z * (dv + 2) + c];
+		}
+		out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
 	}
 }
 
@@ -590,23 +674,58 @@ extern "C" int yalm_kv_pool_rows(float *key_pool, float *value_pool, const void 
 	return (int)cudaGetLastError();
 }
 
-extern "C" int yalm_attn_window_pool(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring, const float *key_pool,
-                                     const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks, int window,
-                                     int pool, float scale, int cache_f32, int pos0, const int *ctl, yalm_stream_t s) {
-	if (!out || !q || !key_ring || !value_ring || n < 1 || n_kv < 1 || n_heads % n_kv || dv > 32 * kAttnMaxDvc || (pool > 0 && (!key_pool || !value_pool)))
-		return YALM_EINVAL;
-	const size_t smem = sizeof(float) * (((dk + 7) & ~7) + kAttnWarps * dv + kAttnWarps * 2);
+// Floats of workspace yalm_attn_window_pool wants for value size dv (split partials of decode-sized calls).
+extern "C" size_t yalm_attn_window_pool_workspace(int dv) {
+	return (size_t)kAttnMaxParts * (dv + 2);
+}
+
+template <typename CT, int R, int DVC>
+static int launch_attn_wp(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, float *ws,
+                          int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool, float scale, int nsplit,
+                          int pos0, const int *ctl, cudaStream_t st) {
+	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
+	const size_t smem = sizeof(float) * ((size_t)R * ((dk + 7) & ~7) + (size_t)kAttnWarps * R * dv + kAttnWarps * R * 2);
 	if (smem > 48 * 1024) return YALM_EINVAL;
-	const dim3 grid(n_heads, n);
-	cudaStream_t st = (cudaStream_t)s;
-	if (cache_f32)
-		attn_window_pool_kernel<float><<<grid, kAttnWarps * 32, smem, st>>>(out, ldo, q, ldq, (const float *)key_ring, (const float *)value_ring, key_pool,
-		                                                                    value_pool, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale, pos0, ctl);
-	else
-		attn_window_pool_kernel<__nv_bfloat16><<<grid, kAttnWarps * 32, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)key_ring,
-		                                                                            (const __nv_bfloat16 *)value_ring, key_pool, value_pool, n_heads, n_kv, dk,
-		                                                                            dv, ring, max_blocks, window, pool, scale, pos0, ctl);
+	attn_window_pool_kernel<CT, R, DVC><<<dim3(n_kv * hg, n, nsplit), kAttnWarps * 32, smem, st>>>(
+	    out, ldo, q, ldq, (const CT *)kr, (const CT *)vr, kp, vp, nsplit > 1 ? ws : nullptr, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale,
+	    pos0, ctl);
+	if (nsplit > 1) attn_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit);
 	return (int)cudaGetLastError();
+}
+
+// workspace: yalm_attn_window_pool_workspace(dv) floats, or null (never split).  context: the most positions a sequence
+// reaches (bounds the number of keys when the position lives on the device); 0: unknown.
+extern "C" int yalm_attn_window_pool(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring, const float *key_pool,
+                                     const float *value_pool, float *workspace, int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks,
+                                     int window, int pool, float scale, int cache_f32, int context, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!out || !q || !key_ring || !value_ring || n < 1 || n_kv < 1 || n_heads % n_kv || dv > 256 || (pool > 0 && (!key_pool || !value_pool)))
+		return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	const int rep = n_heads / n_kv, R = rep >= 2 ? 4 : 1, hg = (rep + R - 1) / R;
+	// few CTAs (decoding): split the keys so that every SM has work; the count depends on shapes only, never on the position
+	int nsplit = 1;
+	const int ctas = n_kv * hg * n;
+	if (workspace && ctas < 296) {
+		const int most_keys = window > 0 ? window + (pool > 0 ? max_blocks : 0) : (context > 0 ? context : ring);
+		const int tiles = (most_keys + 31) / 32;
+		nsplit = std::min({(296 + ctas - 1) / ctas, std::max(1, tiles / 4), std::max(1, kAttnMaxParts / (n * n_heads)), 64});
+	}
+#define ATTN_CASE(CT, R_, DVC_)                                                                                                       \
+	return launch_attn_wp<CT, R_, DVC_>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring, max_blocks, \
+	                                    window, pool, scale, nsplit, pos0, ctl, st)
+#define ATTN_DVC(CT, R_)                                                                                                              \
+	if (dv <= 64) ATTN_CASE(CT, R_, 2);                                                                                               \
+	else if (dv <= 128) ATTN_CASE(CT, R_, 4);                                                                                         \
+	else ATTN_CASE(CT, R_, 8)
+	if (cache_f32) {
+		if (R == 1) { ATTN_DVC(float, 1); }
+		else { ATTN_DVC(float, 4); }
+	} else {
+		if (R == 1) { ATTN_DVC(__nv_bfloat16, 1); }
+		else { ATTN_DVC(__nv_bfloat16, 4); }
+	}
+#undef ATTN_DVC
+#undef ATTN_CASE
 }
 
 extern "C" int yalm_norm_residual_rows(float *x, const float *y, int ldy, int nsum, const float *w, float w_offset, float eps, int n, int dim,

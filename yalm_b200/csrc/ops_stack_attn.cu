@@ -1,0 +1,235 @@
+// Windowed attention with pooled blocks for many query rows (a portion of a prompt) over the bf16 key / value rings, on the
+// tensor cores.  Same visibility rule and the same single softmax as ops_stack.cu's attn_window_pool_kernel, which remains
+// the route for decode-sized calls, the fp32 cache and other head sizes.
+//
+// grid (ceil(n / 64), heads), 4 warps x 16 query rows.  Key tiles of 64 go through shared memory: first the pooled blocks
+// 0 .. nb(last row) - 1 (fp32 means, rounded to bf16 as they are staged), then the tokens lo(first row) .. last row from
+// their ring slots.  S = Q K^T and O += P V on mma.sync.m16n8k16 (bf16 in, fp32 accumulate); scores, running max and sum,
+// and the weights are fp32, the weights are rounded to bf16 only as the operand of P V.  Per row the mask is an interval
+// of the tile's key indices: blocks [0, nb(i)) or tokens [lo(i), i].
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+
+namespace yalm {
+namespace stack {
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+	asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+	asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+	             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+	             : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+	asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+	             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+	             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
+	const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+	return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                                   const __nv_bfloat16 *__restrict__ kc, const __nv_bfloat16 *__restrict__ vc,
+                                                                   const float *__restrict__ kp, const float *__restrict__ vp, int n, int n_heads, int n_kv,
+                                                                   int ring, int max_blocks, int window, int pool, float scale, int pos0,
+                                                                   const int *__restrict__ ctl) {
+	constexpr int LDK = DK + 8, LDV = DV + 8; // padded rows: 16 bytes of skew keep ldmatrix conflict-free
+	constexpr int KS = DK / 16;               // k-steps of Q K^T
+	constexpr int OT = DV / 8;                // 8-wide output tiles of P V
+	extern __shared__ __align__(16) __nv_bfloat16 smb[];
+	__nv_bfloat16 *Qs = smb, *Ks = Qs + 64 * LDK, *Vs = Ks + 64 * LDK;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int h = blockIdx.y, g = h / (n_heads / n_kv), i0 = blockIdx.x * 64;
+	const int p0 = ctl ? ctl[CTL_POS] : pos0;
+	const __nv_bfloat16 *kbase = kc + (size_t)g * ring * DK, *vbase = vc + (size_t)g * ring * DV;
+	const float *kpb = kp ? kp + (size_t)g * max_blocks * DK : nullptr, *vpb = vp ? vp + (size_t)g * max_blocks * DV : nullptr;
+	// Q tile: fp32 -> bf16 (rows past n: zeros)
+	for (int c = threadIdx.x; c < 64 * (DK / 4); c += 128) {
+		const int r = c / (DK / 4), d = (c % (DK / 4)) * 4;
+		float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+		if (i0 + r < n) v = *reinterpret_cast<const float4 *>(q + (size_t)(i0 + r) * ldq + (size_t)h * DK + d);
+		uint2 pk;
+		pk.x = pack_bf2(v.x, v.y), pk.y = pack_bf2(v.z, v.w);
+		*reinterpret_cast<uint2 *>(Qs + r * LDK + d) = pk;
+	}
+	__syncthreads();
+	uint32_t qf[KS][4];
+	{
+		const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, cofs = (lane >> 4) * 8;
+#pragma unroll
+		for (int ks = 0; ks < KS; ++ks) ldsm_x4(qf[ks], (uint32_t)__cvta_generic_to_shared(Qs + r * LDK + ks * 16 + cofs));
+	}
+	float o[OT][4];
+#pragma unroll
+	for (int t = 0; t < OT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+	float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f; // rows lane / 4 and lane / 4 + 8 of the warp's 16
+	const int rA = i0 + warp * 16 + (lane >> 2), rB = rA + 8;
+	// positions (rows past n repeat the last valid row: finite values that are never stored)
+	const int iA = p0 + min(rA, n - 1), iB = p0 + min(rB, n - 1);
+	const int i_first = p0 + i0, i_last = p0 + min(i0 + 63, n - 1);
+	auto lo_of = [&](int i) { return window > 0 ? max(0, i - window + 1) : 0; };
+	auto nb_of = [&](int i) { return (window > 0 && pool > 0 && i - window + 1 >= pool) ? (i - window + 1) / pool : 0; };
+	const int loA = lo_of(iA), loB = lo_of(iB), nbA = nb_of(iA), nbB = nb_of(iB);
+	const int nb_max = nb_of(i_last), lo_min = lo_of(i_first);
+	const int pooled_tiles = (nb_max + 63) / 64, token_tiles = (i_last - lo_min) / 64 + 1;
+	for (int tt = 0; tt < pooled_tiles + token_tiles; ++tt) {
+		const bool pooled = tt < pooled_tiles;
+		const int base = pooled ? tt * 64 : lo_min + (tt - pooled_tiles) * 64; // index of the tile's first key: block or position
+		__syncthreads(); // the previous tile's reads are done
+		if (pooled) {
+			for (int c = threadIdx.x; c < 64 * (DK / 8); c += 128) {
+				const int r = c / (DK / 8), d = (c % (DK / 8)) * 8;
+				uint4 pk = make_uint4(0, 0, 0, 0);
+				if (base + r < nb_max) {
+					const float4 a = *reinterpret_cast<const float4 *>(kpb + (size_t)(base + r) * DK + d), b = *reinterpret_cast<const float4 *>(kpb + (size_t)(base + r) * DK + d + 4);
+					pk.x = pack_bf2(a.x, a.y), pk.y = pack_bf2(a.z, a.w), pk.z = pack_bf2(b.x, b.y), pk.w = pack_bf2(b.z, b.w);
+				}
+				*reinterpret_cast<uint4 *>(Ks + r * LDK + d) = pk;
+			}
+			for (int c = threadIdx.x; c < 64 * (DV / 8); c += 128) {
+				const int r = c / (DV / 8), d = (c % (DV / 8)) * 8;
+				uint4 pk = make_uint4(0, 0, 0, 0);
+				if (base + r < nb_max) {
+					const float4 a = *reinterpret_cast<const float4 *>(vpb + (size_t)(base + r) * DV + d), b = *reinterpret_cast<const float4 *>(vpb + (size_t)(base + r) * DV + d + 4);
+					pk.x = pack_bf2(a.x, a.y), pk.y = pack_bf2(a.z, a.w), pk.z = pack_bf2(b.x, b.y), pk.w = pack_bf2(b.z, b.w);
+				}
+				*reinterpret_cast<uint4 *>(Vs + r * LDV + d) = pk;
+			}
+		} else {
+			for (int c = threadIdx.x; c < 64 * (DK / 8); c += 128) {
+				const int r = c / (DK / 8), d = (c % (DK / 8)) * 8;
+				uint4 pk = make_uint4(0, 0, 0, 0);
+				if (base + r <= i_last) pk = *reinterpret_cast<const uint4 *>(kbase + (size_t)((base + r) % ring) * DK + d);
+				*reinterpret_cast<uint4 *>(Ks + r * LDK + d) = pk;
+			}
+			for (int c = threadIdx.x; c < 64 * (DV / 8); c += 128) {
+				const int r = c / (DV / 8), d = (c % (DV / 8)) * 8;
+				uint4 pk = make_uint4(0, 0, 0, 0);
+				if (base + r <= i_last) pk = *reinterpret_cast<const uint4 *>(vbase + (size_t)((base + r) % ring) * DV + d);
+				*reinterpret_cast<uint4 *>(Vs + r * LDV + d) = pk;
+			}
+		}
+		__syncthreads();
+		// ---- S = Q K^T: 8 key tiles of 8 ----
+		float s[8][4];
+#pragma unroll
+		for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+		{
+			const int kr = (lane & 7) + (lane >> 4) * 8, kcofs = ((lane >> 3) & 1) * 8;
+#pragma unroll
+			for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+				for (int t = 0; t < 8; t += 2) {
+					uint32_t b[4];
+					ldsm_x4(b, (uint32_t)__cvta_generic_to_shared(Ks + (t * 8 + kr) * LDK + ks * 16 + kcofs));
+					mma_bf16(s[t], qf[ks], b[0], b[1]);
+					mma_bf16(s[t + 1], qf[ks], b[2], b[3]);
+				}
+		}
+		// ---- scale, interval mask, online softmax (fp32) ----
+		const int minA = pooled ? 0 : loA, maxA = pooled ? nbA - 1 : iA, minB = pooled ? 0 : loB, maxB = pooled ? nbB - 1 : iB;
+		float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+		for (int t = 0; t < 8; ++t) {
+			const int key = base + t * 8 + (lane & 3) * 2;
+			s[t][0] = (key >= minA && key <= maxA) ? s[t][0] * scale : -INFINITY;
+			s[t][1] = (key + 1 >= minA && key + 1 <= maxA) ? s[t][1] * scale : -INFINITY;
+			s[t][2] = (key >= minB && key <= maxB) ? s[t][2] * scale : -INFINITY;
+			s[t][3] = (key + 1 >= minB && key + 1 <= maxB) ? s[t][3] * scale : -INFINITY;
+			mxA = fmaxf(mxA, fmaxf(s[t][0], s[t][1]));
+			mxB = fmaxf(mxB, fmaxf(s[t][2], s[t][3]));
+		}
+		mxA = fmaxf(mxA, __shfl_xor_sync(kFull, mxA, 1)), mxA = fmaxf(mxA, __shfl_xor_sync(kFull, mxA, 2));
+		mxB = fmaxf(mxB, __shfl_xor_sync(kFull, mxB, 1)), mxB = fmaxf(mxB, __shfl_xor_sync(kFull, mxB, 2));
+		const float nA = fmaxf(m0, mxA), nB = fmaxf(m1, mxB);
+		// a row may see nothing yet (its first visible key lies in a later tile): keep its state empty without producing NaNs
+		const float eA = nA == -INFINITY ? 0.f : nA, eB = nB == -INFINITY ? 0.f : nB;
+		const float cA = m0 == -INFINITY ? 0.f : expf(m0 - eA), cB = m1 == -INFINITY ? 0.f : expf(m1 - eB);
+		m0 = nA, m1 = nB;
+		l0 *= cA, l1 *= cB;
+#pragma unroll
+		for (int t = 0; t < OT; ++t) o[t][0] *= cA, o[t][1] *= cA, o[t][2] *= cB, o[t][3] *= cB;
+		uint32_t pf[4][4]; // P as A fragments: key steps of 16
+#pragma unroll
+		for (int t = 0; t < 8; ++t) {
+			const float p0v = expf(s[t][0] - eA), p1v = expf(s[t][1] - eA), p2v = expf(s[t][2] - eB), p3v = expf(s[t][3] - eB);
+			l0 += p0v + p1v, l1 += p2v + p3v;
+			pf[t >> 1][(t & 1) * 2] = pack_bf2(p0v, p1v);
+			pf[t >> 1][(t & 1) * 2 + 1] = pack_bf2(p2v, p3v);
+		}
+		// ---- O += P V ----
+		{
+			const int vr = (lane & 7) + ((lane >> 3) & 1) * 8, vcofs = (lane >> 4) * 8;
+#pragma unroll
+			for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+				for (int t = 0; t < OT; t += 2) {
+					uint32_t b[4];
+					ldsm_x4_t(b, (uint32_t)__cvta_generic_to_shared(Vs + (kk * 16 + vr) * LDV + t * 8 + vcofs));
+					mma_bf16(o[t], pf[kk], b[0], b[1]);
+					mma_bf16(o[t + 1], pf[kk], b[2], b[3]);
+				}
+		}
+	}
+	l0 += __shfl_xor_sync(kFull, l0, 1), l0 += __shfl_xor_sync(kFull, l0, 2);
+	l1 += __shfl_xor_sync(kFull, l1, 1), l1 += __shfl_xor_sync(kFull, l1, 2);
+#pragma unroll
+	for (int t = 0; t < OT; ++t) {
+		const int d = h * DV + t * 8 + (lane & 3) * 2;
+		if (rA < n) *reinterpret_cast<float2 *>(out + (size_t)rA * ldo + d) = make_float2(o[t][0] / l0, o[t][1] / l0);
+		if (rB < n) *reinterpret_cast<float2 *>(out + (size_t)rB * ldo + d) = make_float2(o[t][2] / l1, o[t][3] / l1);
+	}
+}
+
+template <int DK, int DV>
+static int launch_mma(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, int n, int n_heads,
+                      int n_kv, int ring, int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, cudaStream_t st) {
+	const size_t smem = sizeof(__nv_bfloat16) * (2 * 64 * (DK + 8) + 64 * (DV + 8));
+	static bool configured = false;
+	if (!configured && smem > 48 * 1024) {
+		YALM_TRY(cudaFuncSetAttribute(attn_window_pool_mma_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+		configured = true;
+	}
+	attn_window_pool_mma_kernel<DK, DV><<<dim3((n + 63) / 64, n_heads), 128, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)kr, (const __nv_bfloat16 *)vr,
+	                                                                                   kp, vp, n, n_heads, n_kv, ring, max_blocks, window, pool, scale, pos0,
+	                                                                                   ctl);
+	return (int)cudaGetLastError();
+}
+
+} // namespace stack
+} // namespace yalm
+
+using namespace yalm::stack;
+
+// 1 when yalm_attn_window_pool_mma has a kernel for these head sizes (bf16 rings only).
+extern "C" int yalm_attn_window_pool_mma_shape(int dk, int dv) {
+	return (dk == 64 || dk == 128) && (dv == 32 || dv == 64 || dv == 128);
+}
+
+// The tensor-core route of yalm_attn_window_pool: bf16 key / value rings, head sizes of yalm_attn_window_pool_mma_shape,
+// q rows and out rows 16-byte aligned (ldq, ldo multiples of 4 floats).
+extern "C" int yalm_attn_window_pool_mma(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring,
+                                         const float *key_pool, const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring,
+                                         int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!out || !q || !key_ring || !value_ring || n < 1 || n_kv < 1 || n_heads % n_kv || (pool > 0 && (!key_pool || !value_pool)) || ldq % 4 || ldo % 2 ||
+	    ((uintptr_t)q & 15) || ((uintptr_t)out & 7) || !yalm_attn_window_pool_mma_shape(dk, dv))
+		return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+#define MMA_CASE(DK_, DV_)                                                                                                            \
+	if (dk == DK_ && dv == DV_)                                                                                                       \
+	return launch_mma<DK_, DV_>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, n, n_heads, n_kv, ring, max_blocks, window, pool, scale, pos0, \
+	                            ctl, st)
+	MMA_CASE(64, 32);
+	MMA_CASE(64, 64);
+	MMA_CASE(64, 128);
+	MMA_CASE(128, 32);
+	MMA_CASE(128, 64);
+	MMA_CASE(128, 128);
+#undef MMA_CASE
+	return YALM_EINVAL;
+}

@@ -170,6 +170,7 @@ struct Model::StackScratch {
 	float *x = nullptr, *qkv = nullptr, *vfirst = nullptr, *att = nullptr, *y = nullptr, *gu = nullptr, *h = nullptr, *wts = nullptr, *xn = nullptr,
 	      *logits = nullptr, *probs = nullptr;
 	void *a16 = nullptr;
+	float *attn_ws = nullptr; // split partials of decode-sized attention calls
 	int *ids = nullptr, *tokens = nullptr, *want = nullptr, *targets = nullptr;
 	std::vector<Placement> placements; // filled by build_stack, consumed by cuda_stack
 	~StackScratch() { cudaFree(arena); }
@@ -315,7 +316,8 @@ void Model::cuda_stack(int device) {
 	             {(void **)&S.gu, 4 * cap * 2 * ff},     {(void **)&S.h, 4 * cap * top * ff},    {(void **)&S.wts, 4 * cap * top},
 	             {(void **)&S.xn, 4 * cap * W},          {(void **)&S.logits, 4 * cap * (size_t)s.vocab}, {(void **)&S.probs, 4 * cap},
 	             {(void **)&S.a16, 2 * cap * top * kmax}, {(void **)&S.ids, 4 * cap * top},       {(void **)&S.tokens, 4 * cap},
-	             {(void **)&S.want, 4 * cap},            {(void **)&S.targets, 4 * cap}};
+	             {(void **)&S.want, 4 * cap},            {(void **)&S.targets, 4 * cap},
+	             {(void **)&S.attn_ws, 4 * yalm_attn_window_pool_workspace(256)}};
 	size_t total = 0;
 	for (auto &sl : slots) total += pad(sl.bytes);
 	if (cudaMalloc((void **)&S.arena, total) != cudaSuccess) die("device allocation failed (pass scratch)");
@@ -339,7 +341,14 @@ static int stack_linear(Model &, const Config &c, void *a16, float *y, int ldy, 
 		ST_TRY(yalm_cast_rows16(a16, x, ldx, M, K, dt == YALM_BF16, st));
 		return yalm_gemm_16(y, ldy, a16, w, M, N, K, 0, dt == YALM_BF16, alpha, st);
 	}
+	// one row: the streaming GEMV of the .yalm decode path (x staged in shared memory, 16 weight loads in flight per lane)
+	if (M == 1 && K % 8 == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0) return yalm_gemv_scaled(y, x, w, K, N, dt, alpha, st);
 	return yalm_linear_rows(y, ldy, x, ldx, w, dt, M, N, K, alpha, st);
+}
+
+static bool attn_mma_off() { // YALM_STACK_ATTN_MMA=0: A/B against the SIMT kernel
+	static const bool off = [] { const char *e = getenv("YALM_STACK_ATTN_MMA"); return e && e[0] == '0'; }();
+	return off;
 }
 
 int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want) {
@@ -361,8 +370,13 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 		                          L.ring, sp.norm_eps, f32, pos0, ctl, st));
 		if (m.pool > 0)
 			ST_TRY(yalm_kv_pool_rows(L.kpool, L.vpool, L.kring, L.vring, n, m.kv_heads, m.dim, m.vdim, L.ring, m.pool, L.max_blocks, f32, pos0, ctl, st));
-		ST_TRY(yalm_attn_window_pool(S.att, no, S.qkv, ld, L.kring, L.vring, L.kpool, L.vpool, n, m.heads, m.kv_heads, m.dim, m.vdim, L.ring,
-		                             L.max_blocks, m.window, m.pool, m.scale, f32, pos0, ctl, st));
+		// many rows over bf16 rings: tensor-core attention; decode-sized calls, the fp32 cache and other head sizes: the SIMT kernel
+		if (!f32 && n >= 16 && ld % 4 == 0 && no % 2 == 0 && yalm_attn_window_pool_mma_shape(m.dim, m.vdim) && !attn_mma_off())
+			ST_TRY(yalm_attn_window_pool_mma(S.att, no, S.qkv, ld, L.kring, L.vring, L.kpool, L.vpool, n, m.heads, m.kv_heads, m.dim, m.vdim, L.ring,
+			                                 L.max_blocks, m.window, m.pool, m.scale, pos0, ctl, st));
+		else
+		ST_TRY(yalm_attn_window_pool(S.att, no, S.qkv, ld, L.kring, L.vring, L.kpool, L.vpool, S.attn_ws, n, m.heads, m.kv_heads, m.dim, m.vdim, L.ring,
+		                             L.max_blocks, m.window, m.pool, m.scale, f32, c.max_seq_len, pos0, ctl, st));
 		ST_TRY(stack_linear(*this, c, S.a16, S.y, W, S.att, no, L.wo, n, W, no, 1.f, st));
 		ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, 1, L.norm1, woff, sp.norm_eps, n, W, st));
 		// ---- feed-forward ----

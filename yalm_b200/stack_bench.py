@@ -1,0 +1,184 @@
+"""`bench.py --workload retezen-sizes`: prefill and decode throughput of the Retezen design at sizes that resemble a real
+model's layers (random weights, bf16), beside the library's closest existing model at equal size (the Llama / Mixtral style
+block of the `.yalm` models: same width, heads, head size, feed-forward size, experts, layer count, fp16 weights).
+
+Per size and feed-forward kind it reports
+  prefill tok/s   a `context`-token prompt through Model::forward_batch (host-timed around the synchronous calls)
+  decode tok/s    greedy steps at the end of that context through Model::generate (CUDA events on the launching stream)
+and the share of the HBM / tensor rooflines they reach: decode against the bytes one token must read (Config::active_bytes'
+arithmetic: the layer's matrices, the window of keys and values, the pooled blocks), prefill against 2 x parameters x
+tokens + attention FLOP.  One JSON line with a `sizes` list; the contract keys carry the first size's decode number.
+"""
+import json
+import os
+import shutil
+import struct
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# name: width, heads, kv_heads, head size, window, pool, feed-forward size, experts, top, layers, vocab
+SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, pool=64, ff=8192, moe_ff=2048, experts=8, top=2, layers=4, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, pool=64, ff=14336, moe_ff=3584, experts=8, top=2, layers=3, vocab=32000),
+}
+CONTEXT = 4096
+
+
+def _bf16(a):
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def write_retezen(folder, z, kind, context):
+    """A checkpoint directory of the given size; matrices are tiled from one random block (values only matter for timing
+    through the router's choices, which stay spread because every expert's rows differ by a shift)."""
+    os.makedirs(folder, exist_ok=True)
+    rng = np.random.default_rng(1)
+    block = _bf16(rng.standard_normal(1 << 22).astype(np.float32) * 0.02)
+    W, H, G, D = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0} if kind == "dense" else \
+        {"kind": "moe", "expert": {"ff": z["moe_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    layer = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "mask": {"size": z["window"], "pool": z["pool"]},
+                                            "scale": D ** -0.5, "v_mix": True}, "mlp": mlp}
+    cfg = {"architecture": "Retezen", "width": W, "vocab": z["vocab"], "max_positions": context, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+           "layers": [layer] * z["layers"]}
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    shapes = {"embed": (z["vocab"], W), "pos": (context, W), "final.norm": (W,), "head": (z["vocab"], W)}
+    for i in range(z["layers"]):
+        p = "l%d." % i
+        shapes.update({p + "norm1": (W,), p + "norm2": (W,), p + "mix.q": (H * D, W), p + "mix.k": (G * D, W), p + "mix.v": (G * D, W),
+                       p + "mix.o": (W, H * D), p + "mix.q.norm": (H * D,), p + "mix.k.norm": (G * D,), p + "mix.vmix": ()})
+        if kind == "dense":
+            shapes.update({p + "mlp.gate": (z["ff"], W), p + "mlp.up": (z["ff"], W), p + "mlp.down": (W, z["ff"])})
+        else:
+            shapes[p + "mlp.router"] = (z["experts"], W)
+            for e in range(z["experts"]):
+                shapes.update({p + "mlp.e%d.gate" % e: (z["moe_ff"], W), p + "mlp.e%d.up" % e: (z["moe_ff"], W), p + "mlp.e%d.down" % e: (W, z["moe_ff"])})
+    header, off = {}, 0
+    for name, shp in shapes.items():
+        n = int(np.prod(shp)) if shp else 1
+        header[name] = {"dtype": "BF16", "shape": list(shp), "data_offsets": [off, off + 2 * n]}
+        off += 2 * n
+    h = json.dumps(header).encode()
+    h += b" " * (-len(h) % 8)
+    one = _bf16(np.ones(1, np.float32))[0]
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h)
+        for k, (name, shp) in enumerate(shapes.items()):
+            n = int(np.prod(shp)) if shp else 1
+            if name.endswith(".q.norm") or name.endswith(".k.norm"):
+                f.write(np.full(n, one, np.uint16).tobytes())
+            elif len(shp) < 2:
+                f.write(block[:n].tobytes())
+            else:
+                f.write(np.resize(np.roll(block, 7919 * k), n).tobytes())
+    return cfg
+
+
+def retezen_numbers(z, kind):
+    """-> (weight parameters per token in the layers and head, decode bytes per token at CONTEXT, prefill FLOP per token)"""
+    W, H, G, D = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    attn = (2 * H * D + 2 * G * D) * W
+    ffn = 3 * z["ff"] * W if kind == "dense" else z["top"] * 3 * z["moe_ff"] * W + z["experts"] * W
+    params = z["layers"] * (attn + ffn) + z["vocab"] * W
+    seen = min(CONTEXT, z["window"])
+    blocks = max(0, (CONTEXT - z["window"]) // z["pool"])
+    kv = z["layers"] * (seen * 2 * G * D * 2 + blocks * 2 * G * D * 4)
+    flop = 2.0 * (params - z["vocab"] * W) + 4.0 * z["layers"] * H * D * (seen + blocks)
+    return params, 2 * params + kv, flop
+
+
+def run(args, base, emit, write_yalm, shm_path, ClockSampler):
+    import torch
+    from yalm_b200 import api
+    from yalm_b200 import yalm_file as yf
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(pk)) if os.path.exists(pk) else {"hbm_gbs": 6650.0, "bf16_tflops_sustained": 1400.0}
+    hbm, tflops = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops_sustained"])
+    steps = max(8, min(args.steps, 128))
+    clocks = ClockSampler(0)
+    clocks.start()
+    out, launches = [], 0
+    for name, z in SIZES.items():
+        for kind in ("dense", "moe"):
+            ids = [(i * 7919 + 1) % z["vocab"] for i in range(CONTEXT)]
+            row = {"size": name, "ffn": kind, "width": z["width"], "layers": z["layers"], "context": CONTEXT, "window": z["window"], "pool": z["pool"]}
+            # ---- the new design ----
+            folder = shm_path("yalm_bench_retezen_%s_%s_%d" % (name, kind, os.getpid()))
+            try:
+                write_retezen(folder, z, kind, CONTEXT + steps + args.warmup + 8)
+                model = api.Model(folder, 0, api.BF16).cuda(0)
+            finally:
+                shutil.rmtree(folder, ignore_errors=True)
+            st = api.InferenceState(model)
+            st.forward_batch(ids[:1024], 0)                     # warm-up (sizes kernels, first-use set-up)
+            st.end_sequence()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            st.forward_batch(ids[:-1], 0)
+            t_pre = time.perf_counter() - t0
+            st.generate_greedy(ids[-1], CONTEXT - 1, max(3, args.warmup))   # first step eager + graph capture, untimed
+            pos = CONTEXT - 1 + max(3, args.warmup)
+            st.generate_greedy(ids[0], pos, steps)
+            t_dec = st.device_ms / 1e3
+            params, dec_bytes, pre_flop = retezen_numbers(z, kind)
+            launches += steps * model.launches()
+            row["retezen"] = {"prefill_tok_s": (CONTEXT - 1) / t_pre, "decode_tok_s": steps / t_dec,
+                              "prefill_frac_of_measured_bf16": pre_flop * (CONTEXT - 1) / t_pre / 1e12 / tflops,
+                              "decode_frac_of_measured_hbm": dec_bytes * steps / t_dec / 1e9 / hbm, "decode_bytes_per_token": dec_bytes,
+                              "launches_per_token": model.launches()}
+            st.close()
+            model.close()
+            # ---- the closest existing model at equal size: the .yalm Llama / Mixtral block, fp16 ----
+            arch = yf.Arch(z["width"], z["ff"] if kind == "dense" else z["moe_ff"], z["dim"], z["layers"], z["heads"], z["kv_heads"], z["vocab"],
+                           CONTEXT + 256, 10000.0, n_experts=z["experts"] if kind == "moe" else 0, n_experts_active=z["top"] if kind == "moe" else 0,
+                           name="equal-size-%s-%s" % (name, kind))
+            path = shm_path("yalm_bench_equal_%s_%s_%d.yalm" % (name, kind, os.getpid()))
+            write_yalm(path, arch, "fp16")
+            try:
+                model = api.Model(path, CONTEXT + 256).cuda(0)
+            finally:
+                os.unlink(path)
+            st = api.InferenceState(model)
+            cap = model.batch_capacity()
+            ref = {"whole_token_kernel": model.uses_megakernel(), "launches_per_token": model.launches()}
+            if cap:
+                st.forward_batch(ids[:cap], 0)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for p in range(0, CONTEXT - 1, cap):
+                    st.forward_batch(ids[p:min(p + cap, CONTEXT - 1)], p)
+                ref["prefill_tok_s"] = (CONTEXT - 1) / (time.perf_counter() - t0)
+            else:                                               # no batched pass for this model: the token loop hydrates
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for p in range(256):
+                    st.forward(ids[p], p, api.MODE_HYDRATE)
+                torch.cuda.synchronize()
+                ref["prefill_tok_s"] = 256 / (time.perf_counter() - t0)
+                ref["prefill_note"] = "token loop (this model has no batched pass)"
+                for p in range(256, CONTEXT - 1, 1):            # fill the context for the decode measurement
+                    st.forward(ids[p], p, api.MODE_HYDRATE)
+            st.generate_greedy(ids[-1], CONTEXT - 1, max(3, args.warmup))
+            st.generate_greedy(ids[0], CONTEXT - 1 + max(3, args.warmup), steps)
+            ref["decode_tok_s"] = steps / (st.device_ms / 1e3)
+            full_kv = z["layers"] * CONTEXT * 2 * z["kv_heads"] * z["dim"] * 2
+            ref["decode_frac_of_measured_hbm"] = (2 * params + full_kv) * ref["decode_tok_s"] / 1e9 / hbm
+            ref["prefill_frac_of_measured_bf16"] = (2.0 * (params - z["vocab"] * z["width"]) + 4.0 * z["layers"] * z["heads"] * z["dim"] * CONTEXT / 2) * \
+                ref["prefill_tok_s"] / 1e12 / tflops
+            row["equal_size_yalm"] = ref
+            out.append(row)
+            st.close()
+            model.close()
+    clk = clocks.stop()
+    first = out[0]["retezen"]
+    emit(dict(base, impl="ours", metric="batch-1 decode tok/s (Retezen, first size; all sizes under `sizes`)", value=first["decode_tok_s"], steps=steps,
+              ms_per_step=1000.0 / first["decode_tok_s"], dtype="bf16", clocks=clk, gpu_launches=launches, sizes=out,
+              e2e={"value": first["decode_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
+                   "note": "device loop: token ids stay on the device, 4 bytes per token come back"},
+              config=dict(base["config"], workload="Retezen at model-like sizes beside the equal-size .yalm block", context=CONTEXT,
+                          l2="inputs larger than L2 (weights streamed per token)")))
