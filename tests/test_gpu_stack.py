@@ -329,6 +329,29 @@ def test_serving_precision(tmp_path):
     rows_close(dec, want[40:])
 
 
+def test_command_line_on_a_checkpoint_directory(tmp_path):
+    import re
+    exe = os.path.join(ROOT, "build", "main")
+    if not os.path.exists(exe):
+        subprocess.check_call(["make", "-s", "-C", ROOT, "cli"])
+    cfg = four_layers()
+    folder, W = checkpoint(tmp_path, cfg, seed=15, sharp=2.0)
+    prompt = tokens_for(cfg, 17)
+    text = " ".join(map(str, prompt))
+    r = subprocess.run([exe, folder, "-m", "completion", "-i", text, "-n", "6", "-t", "0", "-p", "fp32"], capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    ids = [l for l in r.stdout.splitlines() if re.fullmatch(r"(\d+ )+", l)]
+    assert ids and [int(x) for x in ids[-1].split()] == O.greedy(cfg, W, prompt, 6)
+    r = subprocess.run([exe, folder, "-m", "perplexity", "-i", text, "-p", "fp32"], capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lg = O.forward(cfg, W, prompt[:-1])
+    lp = lg - lg.max(1, keepdims=True)
+    lp = lp - np.log(np.exp(lp).sum(1, keepdims=True))
+    want = float(np.exp(-lp[np.arange(16), prompt[1:]].mean()))
+    got = float(re.search(r"perplexity: ([0-9.eE+-]+)", r.stdout).group(1))
+    assert abs(got - want) <= 2e-3 * want, (got, want)
+
+
 def test_trace_runner(tmp_path):
     cfg = four_layers()
     folder, W = checkpoint(tmp_path, cfg, seed=14)

@@ -1,15 +1,20 @@
 // build/main — the reference's command line (src/main.cpp:17-42, 290-429) over the B200 forward pass:
 //
-//   main <checkpoint> [-d cuda|cpu] [-m completion|passkey|perplexity] [-T context] [-i prompt | -f file]
+//   main <checkpoint | checkpoint directory> [-d cuda|cpu] [-m completion|passkey|perplexity] [-T context] [-i prompt | -f file]
 //                     [-n steps] [-t temperature] [-l passkey position]
 //
 // Same flags, the same unique-prefix matching of mode / device names, the same stats blocks.  What differs is
 // underneath: `-d cuda` is the only device (there is no CPU execution path in this library: `-d cpu` is refused), the
 // next token is sampled on the device (4 bytes per token come back instead of vocab * 4), and perplexity scores whole
 // prompt chunks per launch when the model supports the batched prefill path (Model::forward_batch).
+// A checkpoint DIRECTORY (config.json + model.safetensors of a registered layered architecture, arch.h) runs through the
+// same Model / InferenceState / Sampler calls; such a directory carries no tokenizer, so prompts are token ids separated
+// by spaces and the output is printed as ids ("-p fp32" computes in true 32-bit, default: as stored).
 #include "sampler.h"
 #include "tokenizer.h"
 #include "yalm_api.h"
+
+#include <sys/stat.h>
 
 #include <chrono>
 #include <cmath>
@@ -36,6 +41,7 @@ uint64_t now_ms() {
 	      "  -d [cpu,cuda] which device to use (default - cuda; this build has no CPU path and refuses cpu)\n"
 	      "  -m [completion,passkey,perplexity] which mode to run in (default - completion)\n"
 	      "  -T <int> sliding window context length (0 - max)\n"
+	      "  -p [fp32,bf16] checkpoint directories: precision to compute in (default - as stored); prompts are token ids\n"
 	      "\n"
 	      "Perplexity mode options:\n"
 	      "  Choose one:\n"
@@ -58,6 +64,7 @@ struct Options {
 	std::string checkpoint, device = "cuda", mode = "completion", prompt, prompt_path;
 	int context = 0, num_steps = 256, n_junk = 250, passkey_pos = -1;
 	float temperature = 1.0f;
+	int compute_dtype = -1; // checkpoint directories: -p fp32 | bf16
 };
 
 // `given` selects the one of `names` it is a prefix of, first match in list order (src/main.cpp:330-357)
@@ -90,6 +97,11 @@ Options parse(int argc, char **argv) {
 		case 'T': o.context = std::stoi(v); break;
 		case 'l': o.passkey_pos = std::stoi(v); break;
 		case 'n': o.num_steps = o.n_junk = std::stoi(v); break;
+		case 'p':
+			if (std::string(v) == "fp32") o.compute_dtype = YALM_F32;
+			else if (std::string(v) == "bf16") o.compute_dtype = YALM_BF16;
+			else usage();
+			break;
 		default: usage();
 		}
 	}
@@ -102,17 +114,23 @@ struct Session {
 	std::unique_ptr<Model> model;
 	std::unique_ptr<InferenceState> state;
 	std::unique_ptr<Sampler> sampler;
-	std::unique_ptr<Tokenizer> tokenizer;
+	std::unique_ptr<Tokenizer> tokenizer; // null for checkpoint directories: prompts and output are token ids
+	int eos_id = -1, eot_id = -1;
 
 	Session(const Options &o) {
-		if (data.from_file(o.checkpoint) != 0) {
+		struct stat sb;
+		const bool dir = stat(o.checkpoint.c_str(), &sb) == 0 && S_ISDIR(sb.st_mode);
+		if ((dir ? data.from_directory(o.checkpoint) : data.from_file(o.checkpoint)) != 0) {
 			std::cerr << "Error: could not load checkpoint " << o.checkpoint << std::endl;
 			exit(1);
 		}
-		model = std::make_unique<Model>(data, o.context);
+		model = std::make_unique<Model>(data, o.context, dir ? o.compute_dtype : -1);
 		state = std::make_unique<InferenceState>(model->config);
 		sampler = std::make_unique<Sampler>(model->config, now_ms());
-		tokenizer = std::make_unique<Tokenizer>(data);
+		if (!dir) {
+			tokenizer = std::make_unique<Tokenizer>(data);
+			eos_id = tokenizer->eos_id, eot_id = tokenizer->eot_id;
+		}
 		std::cout << "Model active bytes with full context window: " << model->config->active_bytes(model->config->max_seq_len) << std::endl;
 		std::cout << "Using CUDA" << std::endl;
 		model->cuda();
@@ -121,11 +139,29 @@ struct Session {
 		model->forward(*state, 0, 0);  // warm-up, as the reference does (src/main.cpp:66-70)
 	}
 
+	std::string decode_one(int prev, int tok) const { return tokenizer ? tokenizer->decode_one(prev, tok) : std::to_string(tok) + " "; }
+
 	std::vector<int> encode(const std::string &prompt, bool print_ids) {
 		const uint64_t t0 = now_ms();
-		std::vector<int> enc = tokenizer->encode(prompt, true);
+		std::vector<int> enc;
+		if (tokenizer) enc = tokenizer->encode(prompt, true);
+		else {
+			std::istringstream in(prompt);
+			for (long v; in >> v;) {
+				if (v < 0 || v >= model->config->vocab_size) {
+					std::cerr << "Error: token id " << v << " is outside the vocabulary" << std::endl;
+					exit(1);
+				}
+				enc.push_back((int)v);
+			}
+			if (enc.empty()) {
+				std::cerr << "Error: a checkpoint directory has no tokenizer: give the prompt as token ids separated by spaces" << std::endl;
+				exit(1);
+			}
+			print_ids = false;
+		}
 		const double s = (now_ms() - t0) / 1000.0;
-		if (print_ids) std::cout << tokenizer->encoding_to_debug_string(enc) << std::endl;
+		if (print_ids && tokenizer) std::cout << tokenizer->encoding_to_debug_string(enc) << std::endl;
 		printf("Encoding stats: (%zu tokens, throughput: %.5gtok/s, latency: %.5gs/tok, total: %.5gs)\n\n", enc.size(), enc.size() / s,
 		       s / enc.size(), s);
 		return enc;
@@ -141,16 +177,23 @@ void run_completion(const Options &o) {
 	const uint64_t start = now_ms();
 	size_t read_bytes = 0;
 	// hydrate the KV cache with the prompt; only the last position needs logits (src/main.cpp:91-97)
-	for (size_t pos = 0; pos < enc.size(); ++pos) {
-		model.forward(state, enc[pos], (int)pos, pos + 1 == enc.size() ? InferenceMode::OUTPUT_LOGITS : InferenceMode::HYDRATE_KV_CACHE);
-		read_bytes += model.config->active_bytes(pos);
-	}
+	if (model.is_stack()) { // layered models take the whole prompt in one call (walked in portions inside)
+		if (model.forward_batch(state, enc.data(), (int)enc.size(), 0, nullptr, nullptr) != 0) {
+			std::cerr << "Error: the prompt does not fit the model (" << enc.size() << " tokens, limit " << model.config->max_seq_len << ")" << std::endl;
+			exit(1);
+		}
+		read_bytes += model.config->active_bytes(enc.size() - 1);
+	} else
+		for (size_t pos = 0; pos < enc.size(); ++pos) {
+			model.forward(state, enc[pos], (int)pos, pos + 1 == enc.size() ? InferenceMode::OUTPUT_LOGITS : InferenceMode::HYDRATE_KV_CACHE);
+			read_bytes += model.config->active_bytes(pos);
+		}
 	const uint64_t hydrated = now_ms();
 	for (int i = 0; i < num_steps || num_steps == -1; ++i) { // src/main.cpp:102-112
 		const int tok = S.sampler->sample_device(state, o.temperature);
-		std::cout << S.tokenizer->decode_one(enc.back(), tok) << std::flush;
+		std::cout << S.decode_one(enc.back(), tok) << std::flush;
 		enc.push_back(tok);
-		if (tok == S.tokenizer->eos_id || tok == S.tokenizer->eot_id) break;
+		if (tok == S.eos_id || tok == S.eot_id) break;
 		model.forward(state, tok, (int)enc.size() - 1);
 		read_bytes += model.config->active_bytes(enc.size() - 1);
 	}
@@ -207,6 +250,10 @@ void run_perplexity(const Options &o) {
 
 void run_passkey(const Options &o) {
 	Session S(o);
+	if (!S.tokenizer) {
+		std::cerr << "Error: passkey mode builds its prompt from text and needs a checkpoint with a tokenizer" << std::endl;
+		exit(1);
+	}
 	Model &model = *S.model;
 	InferenceState &state = *S.state;
 	const std::string prefix = "There is an important info hidden inside a lot of irrelevant text. "
@@ -231,9 +278,9 @@ void run_passkey(const Options &o) {
 	std::cout << std::endl << suffix << std::flush;
 	for (size_t pos = N; pos < N + 16; ++pos) { // at most 16 greedy steps (src/main.cpp:268-287)
 		const int tok = S.sampler->sample_device(state, 0.f);
-		std::cout << S.tokenizer->decode_one(enc.back(), tok) << std::flush;
+		std::cout << S.decode_one(enc.back(), tok) << std::flush;
 		enc.push_back(tok);
-		if (tok == S.tokenizer->eos_id || tok == S.tokenizer->eot_id) break;
+		if (tok == S.eos_id || tok == S.eot_id) break;
 		model.forward(state, tok, (int)pos);
 	}
 	std::cout << std::endl;

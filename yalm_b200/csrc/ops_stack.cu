@@ -370,7 +370,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
 	const int i = first_pos(ctl, pos0) + m;
 	const int lo = window > 0 ? max(0, i - window + 1) : 0;
 	const int nb = (window > 0 && pool > 0 && i - window + 1 >= pool) ? (i - window + 1) / pool : 0;
-	const int nkeys = nb + (i - lo + 1);
 	for (int e = threadIdx.x; e < R * dkp; e += blockDim.x) {
 		const int r = e / dkp, d = e % dkp;
 		qs[e] = (r < nh && d < dk) ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
@@ -386,47 +385,55 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
 #pragma unroll
 		for (int c = 0; c < DVC; ++c) acc[r][c] = 0.f;
 	}
-	const int ntiles = (nkeys + 31) / 32, per = (ntiles + nsplit - 1) / nsplit;
+	// pooled blocks and tokens occupy separate 32-key tiles, so that a tile's rows are of one kind (fp32 means or cache rows)
+	const int ntok = i - lo + 1, ptiles = (nb + 31) / 32, ntiles = ptiles + (ntok + 31) / 32, per = (ntiles + nsplit - 1) / nsplit;
 	const int t_end = min(ntiles, (z + 1) * per);
 	for (int t = z * per + warp; t < t_end; t += kAttnWarps) {
-		const int t0 = t * 32, u = t0 + lane;
+		const bool pooled = t < ptiles;
+		const int idx0 = pooled ? t * 32 : (t - ptiles) * 32, cnt = min(32, (pooled ? nb : ntok) - idx0);
 		float s[R], p[R];
 #pragma unroll
 		for (int r = 0; r < R; ++r) s[r] = 0.f;
-		if (u < nkeys) {
-			if (u < nb) key_dots_f32<R>(kpb + (size_t)u * dk, qs, dkp, dk, kvec_p, s);
-			else key_dots_any<R>(kbase + (size_t)((lo + u - nb) % ring) * dk, qs, dkp, dk, kvec_c, s);
+		if (lane < cnt) {
+			if (pooled) key_dots_f32<R>(kpb + (size_t)(idx0 + lane) * dk, qs, dkp, dk, kvec_p, s);
+			else key_dots_any<R>(kbase + (size_t)((lo + idx0 + lane) % ring) * dk, qs, dkp, dk, kvec_c, s);
 		}
 #pragma unroll
 		for (int r = 0; r < R; ++r) {
-			const float sv = u < nkeys ? s[r] : -INFINITY;
+			const float sv = lane < cnt ? s[r] : -INFINITY;
 			const float nmx = fmaxf(mx[r], warp_max(sv));     // finite: the tile holds at least one key
 			const float corr = mx[r] == -INFINITY ? 0.f : expf(mx[r] - nmx);
-			p[r] = u < nkeys ? expf(sv - nmx) : 0.f;
+			p[r] = lane < cnt ? expf(sv - nmx) : 0.f;
 			l[r] = l[r] * corr + warp_sum(p[r]);
 			mx[r] = nmx;
 #pragma unroll
 			for (int c = 0; c < DVC; ++c) acc[r][c] *= corr;
 		}
-		const int cnt = min(32, nkeys - t0);
-		for (int kk = 0; kk < cnt; ++kk) {
-			const int uk = t0 + kk;
-			float vv[DVC];
-			if (uk < nb) {
-				const float *vr = vpb + (size_t)uk * dv;
+		// P V: lane = value channel; the value rows of KU keys are fetched before the first multiply (one L2 round trip per KU keys)
+		constexpr int KU = 8;
+		for (int k0 = 0; k0 < cnt; k0 += KU) {
+			float vv[KU][DVC];
 #pragma unroll
-				for (int c = 0; c < DVC; ++c) vv[c] = c * 32 + lane < dv ? vr[c * 32 + lane] : 0.f;
-			} else {
-				const CT *vr = vbase + (size_t)((lo + uk - nb) % ring) * dv;
+			for (int j = 0; j < KU; ++j) {
+				const int kk = min(k0 + j, cnt - 1); // past the end: a repeated row whose weight is zero
+				if (pooled) {
+					const float *vr = vpb + (size_t)(idx0 + kk) * dv;
 #pragma unroll
-				for (int c = 0; c < DVC; ++c) vv[c] = c * 32 + lane < dv ? cache_get(vr, c * 32 + lane) : 0.f;
+					for (int c = 0; c < DVC; ++c) vv[j][c] = c * 32 + lane < dv ? vr[c * 32 + lane] : 0.f;
+				} else {
+					const CT *vr = vbase + (size_t)((lo + idx0 + kk) % ring) * dv;
+#pragma unroll
+					for (int c = 0; c < DVC; ++c) vv[j][c] = c * 32 + lane < dv ? cache_get(vr, c * 32 + lane) : 0.f;
+				}
 			}
 #pragma unroll
-			for (int r = 0; r < R; ++r) {
-				const float pk = __shfl_sync(kFull, p[r], kk);
+			for (int j = 0; j < KU; ++j)
 #pragma unroll
-				for (int c = 0; c < DVC; ++c) acc[r][c] = fmaf(pk, vv[c], acc[r][c]);
-			}
+				for (int r = 0; r < R; ++r) {
+					const float pk = k0 + j < cnt ? __shfl_sync(kFull, p[r], (k0 + j) & 31) : 0.f;
+#pragma unroll
+					for (int c = 0; c < DVC; ++c) acc[r][c] = fmaf(pk, vv[j][c], acc[r][c]);
+				}
 		}
 	}
 #pragma unroll
@@ -707,8 +714,8 @@ extern "C" int yalm_attn_window_pool(float *out, int ldo, const float *q, int ld
 	const int ctas = n_kv * hg * n;
 	if (workspace && ctas < 296) {
 		const int most_keys = window > 0 ? window + (pool > 0 ? max_blocks : 0) : (context > 0 ? context : ring);
-		const int tiles = (most_keys + 31) / 32;
-		nsplit = std::min({(296 + ctas - 1) / ctas, std::max(1, tiles / 4), std::max(1, kAttnMaxParts / (n * n_heads)), 64});
+		const int tiles = (most_keys + 31) / 32 + 1;
+		nsplit = std::min({(296 + ctas - 1) / ctas, std::max(1, (tiles + kAttnWarps - 1) / kAttnWarps), std::max(1, kAttnMaxParts / (n * n_heads)), 64});
 	}
 #define ATTN_CASE(CT, R_, DVC_)                                                                                                       \
 	return launch_attn_wp<CT, R_, DVC_>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring, max_blocks, \
