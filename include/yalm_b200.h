@@ -231,6 +231,25 @@ int yalm_moe_glu_slots(float *h, const float *x, int ldx, const void *wg, const 
 int yalm_moe_down_slots(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top, int ff,
                         int dim, int out_scale, yalm_stream_t s);
 
+/* Experts on the tensor cores (prompt portions): order[j] is the slot (row * top + k) at place j once slots are sorted by
+ * expert.  gather: out16[j] = x[order[j] / top] (* wts[order[j]] if in_scale) as bf16 / fp16; scatter: y[order[j]] = ys[j]
+ * (* wts[order[j]] if out_scale). */
+int yalm_moe_gather_rows16(void *out16, const float *x, int ldx, const int *order, const float *wts, int n_slots, int top, int dim, int bf16,
+                           int in_scale, yalm_stream_t s);
+int yalm_moe_scatter_rows(float *y, int ldy, const float *ys, int lds, const int *order, const float *wts, int n_slots, int dim, int out_scale,
+                          yalm_stream_t s);
+
+/* One-row (decode) products with what follows them fused in, on the streaming GEMV: the CTA that finishes last runs the tail.
+ * yalm_gemv_norm_residual: y = W x (d x n), res += rms(y) (w_offset + nw); gu != 0: x is a (gate | up) row of 2 n floats and
+ * the input is act(g) (u + up_offset).  yalm_gemv_qkv_post: qkv = W x, then yalm_qkv_post_rows for the row and the block mean
+ * if the position completes a block.  counter: a zeroed device word, left zero.  n % 8 == 0 (fp32: 4), 16-byte aligned. */
+int yalm_gemv_norm_residual(float *res, float *y, const float *x, const void *w, const float *nw, float w_offset, float eps, int n, int d,
+                            int dtype, int gu, int act, float act_alpha, float limit, float up_offset, unsigned *counter, yalm_stream_t s);
+int yalm_gemv_qkv_post(float *qkv, const float *x, const void *w, int n, int dtype, void *key_ring, void *value_ring, float *vfirst,
+                       const float *qnorm, const float *knorm, const float *vmix, int vmode, int n_heads, int n_kv, int dk, int dv, int ring,
+                       float eps, int cache_f32, float *key_pool, float *value_pool, int pool, int max_blocks, int pos0, const int *ctl,
+                       unsigned *counter, yalm_stream_t s);
+
 /* ---- (3a) host-pointer test entry points (src/infer.cu:890-1007 semantics) ------------------- */
 int yalm_matmul_host(float *xout, const float *x, const void *w, const float *scale, int n, int d, int dtype);
 int yalm_mha_host(float *xout, float *att, const uint16_t *kb, const uint16_t *vb, const float *q, int head_dim,

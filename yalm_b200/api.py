@@ -35,8 +35,8 @@ SYMBOLS = [
     "yalm_token_probs_host", "yalm_gemm_f16", "yalm_gemm_glu_f16", "yalm_attn_prefill", "yalm_gemm_host",
     "yalm_model_batch_capacity", "yalm_forward_batch", "yalm_generate", "yalm_state_debug_set_launch_seq", "yalm_tokenize", "yalm_detokenize",
     "yalm_embed_rows", "yalm_linear_rows", "yalm_cast_rows16", "yalm_gemm_16", "yalm_qkv_post_rows", "yalm_kv_pool_rows", "yalm_attn_window_pool",
-    "yalm_norm_residual_rows", "yalm_norm_gather_rows", "yalm_glu_act_rows", "yalm_router_topk_rows", "yalm_moe_glu_slots", "yalm_moe_down_slots",
-    "yalm_model_open_dir", "yalm_model_is_stack", "yalm_forward_rows", "yalm_sequence_end", "yalm_stack_read", "yalm_stack_ring_slots", "yalm_attn_window_pool_host", "yalm_gemv_scaled", "yalm_attn_window_pool_mma", "yalm_attn_window_pool_mma_shape", "yalm_attn_window_pool_workspace",
+    "yalm_norm_residual_rows", "yalm_norm_gather_rows", "yalm_glu_act_rows", "yalm_router_topk_rows", "yalm_moe_glu_slots", "yalm_moe_down_slots", "yalm_moe_gather_rows16", "yalm_moe_scatter_rows",
+    "yalm_model_open_dir", "yalm_model_is_stack", "yalm_forward_rows", "yalm_sequence_end", "yalm_stack_read", "yalm_stack_ring_slots", "yalm_attn_window_pool_host", "yalm_gemv_scaled", "yalm_gemv_norm_residual", "yalm_gemv_qkv_post", "yalm_attn_window_pool_mma", "yalm_attn_window_pool_mma_shape", "yalm_attn_window_pool_workspace",
     "yalm_tp_unique_id", "yalm_tp_init", "yalm_tp_finalize", "yalm_tp_shard_plan", "yalm_mega_tile_plan", "yalm_mega_attn_split", "yalm_mega_mma_plan", "yalm_mega_hb_share", "yalm_error_string", "yalm_version",
 ]
 

@@ -815,7 +815,8 @@ int Model::launch_mega(InferenceState &s, int token, int pos, int mode, long lon
 }
 
 int Model::launches_per_forward(InferenceMode mode) const {
-	if (config->stack) { // embed + per layer: qkv, q/k norm + append, [pool], attention, wo, norm + residual, feed-forward (4) [+ final norm, head]
+	if (config->stack && _stack_step_nodes > 0) return _stack_step_nodes; // counted from the captured decode step
+	if (config->stack) { // before any capture, the per-op route: embed + per layer: qkv, q/k norm + append, [pool], attention, wo, norm + residual, feed-forward (4) [+ final norm, head]
 		int n = 1;
 		for (const yalm::LayerSpec &l : config->stack->layers) n += 5 + (l.mix.pool > 0 ? 1 : 0) + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 4);
 		return n + (mode == InferenceMode::OUTPUT_LOGITS ? 2 : 0);

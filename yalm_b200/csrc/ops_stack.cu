@@ -24,54 +24,10 @@
 #include <algorithm>
 
 #include "gemv.cuh"
+#include "stack_rows.cuh"
 
 namespace yalm {
 namespace stack {
-
-// ---- element access ----------------------------------------------------------------------------------------------------
-template <int DT> struct Elem;
-template <> struct Elem<YALM_F32> {
-	using T = float;
-	static constexpr int VEC = 4;
-	__device__ static __forceinline__ float get(const void *p, size_t i) { return static_cast<const float *>(p)[i]; }
-	__device__ static __forceinline__ void unpack(uint4 w, float (&f)[8]) {
-		f[0] = __uint_as_float(w.x), f[1] = __uint_as_float(w.y), f[2] = __uint_as_float(w.z), f[3] = __uint_as_float(w.w);
-	}
-};
-template <> struct Elem<YALM_F16> {
-	using T = __half;
-	static constexpr int VEC = 8;
-	__device__ static __forceinline__ float get(const void *p, size_t i) { return __half2float(static_cast<const __half *>(p)[i]); }
-	__device__ static __forceinline__ void unpack(uint4 w, float (&f)[8]) {
-		const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-		for (int i = 0; i < 4; ++i) {
-			const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&u[i]));
-			f[2 * i] = v.x, f[2 * i + 1] = v.y;
-		}
-	}
-};
-template <> struct Elem<YALM_BF16> {
-	using T = __nv_bfloat16;
-	static constexpr int VEC = 8;
-	__device__ static __forceinline__ float get(const void *p, size_t i) {
-		return __uint_as_float((uint32_t) static_cast<const uint16_t *>(p)[i] << 16);
-	}
-	__device__ static __forceinline__ void unpack(uint4 w, float (&f)[8]) { // bf16 -> fp32 is a 16-bit shift
-		const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-		for (int i = 0; i < 4; ++i) f[2 * i] = __uint_as_float(u[i] << 16), f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
-	}
-};
-
-__device__ __forceinline__ float cache_get(const float *p, size_t i) { return p[i]; }
-__device__ __forceinline__ float cache_get(const __nv_bfloat16 *p, size_t i) {
-	return __uint_as_float((uint32_t) reinterpret_cast<const uint16_t *>(p)[i] << 16);
-}
-__device__ __forceinline__ void cache_put(float *p, size_t i, float v) { p[i] = v; }
-__device__ __forceinline__ void cache_put(__nv_bfloat16 *p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ int first_pos(const int *ctl, int pos0) { return ctl ? ctl[CTL_POS] : pos0; }
 
 // dot(weight row, x) over K elements, result in every lane.  `vec`: the row and x are 16-byte aligned and K % VEC == 0.
 template <int DT>
@@ -106,7 +62,6 @@ __device__ __forceinline__ float warp_dot(const void *w, size_t row_off, const f
 	return warp_sum(acc);
 }
 
-__host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---- embedding ---------------------------------------------------------------------------------------------------------
 template <int DT>
@@ -240,37 +195,9 @@ __global__ void __launch_bounds__(256) qkv_post_rows_kernel(float *__restrict__ 
                                                             int nk, int nv, int dk, int dv, int ring, float eps, int pos0,
                                                             const int *__restrict__ ctl) {
 	__shared__ float red[33];
-	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m, slot = p % ring;
-	float *row = qkv + (size_t)m * ld;
-	float rq = 1.f, rk = 1.f;
-	if (qnorm) {
-		float s = 0.f;
-		for (int e = threadIdx.x; e < nq; e += blockDim.x) s += row[e] * row[e];
-		s = block_sum(s, red);
-		rq = 1.0f / sqrtf(s / nq + eps);
-	}
-	if (knorm) {
-		float s = 0.f;
-		for (int e = threadIdx.x; e < nk; e += blockDim.x) s += row[nq + e] * row[nq + e];
-		s = block_sum(s, red);
-		rk = 1.0f / sqrtf(s / nk + eps);
-	}
-	if (qnorm)
-		for (int e = threadIdx.x; e < nq; e += blockDim.x) row[e] = row[e] * rq * qnorm[e];
-	for (int e = threadIdx.x; e < nk; e += blockDim.x) {
-		float v = row[nq + e];
-		if (knorm) v = v * rk * knorm[e];
-		const int g = e / dk, d = e % dk;
-		cache_put(kc, ((size_t)g * ring + slot) * dk + d, v);
-	}
-	const float lam = vmode == 2 ? vmix[0] : 0.f;
-	for (int e = threadIdx.x; e < nv; e += blockDim.x) {
-		float v = row[nq + nk + e];
-		if (vmode == 1) vfirst[(size_t)m * ldvf + e] = v;
-		else if (vmode == 2) v = (1.0f - lam) * v + lam * vfirst[(size_t)m * ldvf + e];
-		const int g = e / dv, d = e % dv;
-		cache_put(vc, ((size_t)g * ring + slot) * dv + d, v);
-	}
+	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m;
+	qkv_post_row<CT>(qkv + (size_t)m * ld, kc, vc, vfirst ? vfirst + (size_t)m * ldvf : nullptr, qnorm, knorm, vmix, vmode, nq, nk, nv, dk, dv, ring, p % ring,
+	                 eps, red);
 }
 
 // Mean key / value (fp32) of every block of `pool` positions whose last position is one of these rows; the members are read
@@ -279,18 +206,9 @@ template <typename CT>
 __global__ void kv_pool_rows_kernel(float *__restrict__ kp, float *__restrict__ vp, const CT *__restrict__ kc, const CT *__restrict__ vc, int n,
                                     int dk, int dv, int ring, int pool, int max_blocks, int pos0, const int *__restrict__ ctl) {
 	const int p0 = first_pos(ctl, pos0);
-	const int b = p0 / pool + blockIdx.x, g = blockIdx.y; // first block whose end (b * pool + pool - 1) is >= p0
+	const int b = p0 / pool + blockIdx.x; // first block whose end (b * pool + pool - 1) is >= p0
 	if (b * pool + pool > p0 + n || b >= max_blocks) return;
-	const float inv = 1.0f / (float)pool;
-	for (int d = threadIdx.x; d < dk + dv; d += blockDim.x) {
-		float s = 0.f;
-		for (int t = 0; t < pool; ++t) {
-			const int slot = (b * pool + t) % ring;
-			s += d < dk ? cache_get(kc, ((size_t)g * ring + slot) * dk + d) : cache_get(vc, ((size_t)g * ring + slot) * dv + (d - dk));
-		}
-		if (d < dk) kp[((size_t)g * max_blocks + b) * dk + d] = s * inv;
-		else vp[((size_t)g * max_blocks + b) * dv + (d - dk)] = s * inv;
-	}
+	kv_pool_block<CT>(kp, vp, kc, vc, b, blockIdx.y, dk, dv, ring, pool, max_blocks);
 }
 
 // ---- attention: sliding window + pooled blocks, one softmax ------------------------------------------------------------
@@ -326,7 +244,25 @@ __device__ __forceinline__ void key_dots_f32(const float *krow, const float *qs,
 }
 template <int R>
 __device__ __forceinline__ void key_dots_bf16(const __nv_bfloat16 *krow, const float *qs, int dkp, int dk, bool vec, float (&s)[R]) {
-	if (vec) {
+	if (vec && dk % 64 == 0) { // eight 16-byte pieces of the row in flight per lane: one memory round trip per 64 channels
+		for (int d0 = 0; d0 < dk; d0 += 64) {
+			uint4 w[8];
+#pragma unroll
+			for (int j = 0; j < 8; ++j) w[j] = __ldg(reinterpret_cast<const uint4 *>(krow + d0 + 8 * j));
+#pragma unroll
+			for (int j = 0; j < 8; ++j) {
+				float f[8];
+				Elem<YALM_BF16>::unpack(w[j], f);
+				const int d = d0 + 8 * j;
+#pragma unroll
+				for (int r = 0; r < R; ++r) {
+					const float4 q0 = *reinterpret_cast<const float4 *>(qs + r * dkp + d), q1 = *reinterpret_cast<const float4 *>(qs + r * dkp + d + 4);
+					s[r] = fmaf(f[0], q0.x, s[r]), s[r] = fmaf(f[1], q0.y, s[r]), s[r] = fmaf(f[2], q0.z, s[r]), s[r] = fmaf(f[3], q0.w, s[r]);
+					s[r] = fmaf(f[4], q1.x, s[r]), s[r] = fmaf(f[5], q1.y, s[r]), s[r] = fmaf(f[6], q1.z, s[r]), s[r] = fmaf(f[7], q1.w, s[r]);
+				}
+			}
+		}
+	} else if (vec) {
 		for (int d = 0; d < dk; d += 8) {
 			float f[8];
 			Elem<YALM_BF16>::unpack(*reinterpret_cast<const uint4 *>(krow + d), f);
@@ -494,16 +430,7 @@ __global__ void __launch_bounds__(256) norm_residual_rows_kernel(float *__restri
 	__shared__ float red[33];
 	extern __shared__ float ys[]; // dim
 	const int m = blockIdx.x;
-	float ss = 0.f;
-	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
-		float v = 0.f;
-		for (int j = 0; j < nsum; ++j) v += y[((size_t)m * nsum + j) * ldy + e];
-		ys[e] = v;
-		ss += v * v;
-	}
-	ss = block_sum(ss, red);
-	const float r = 1.0f / sqrtf(ss / dim + eps);
-	for (int e = threadIdx.x; e < dim; e += blockDim.x) x[(size_t)m * dim + e] += ys[e] * r * (woff + w[e]);
+	norm_residual_row(x + (size_t)m * dim, y + (size_t)m * nsum * ldy, ldy, nsum, w, woff, eps, dim, ys, red);
 }
 
 // out[r] = rms(x[rows[r]]) * (offset + w)   (rows null: r itself)
@@ -520,14 +447,6 @@ __global__ void __launch_bounds__(256) norm_gather_rows_kernel(float *__restrict
 }
 
 // ---- gated activation ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float glu_value(float g, float u, int act, float alpha, float limit, float up_offset) {
-	if (limit > 0.f) g = fminf(g, limit), u = fminf(fmaxf(u, -limit), limit);
-	float a;
-	if (act == 2) a = g / (1.0f + expf(-alpha * g));      // g * sigmoid(alpha g)
-	else if (act == YALM_ACT_SILU) a = act_silu(g);
-	else a = act_gelu(g);
-	return a * (u + up_offset);
-}
 // h[m, f] = act(gu[m, f]) * (gu[m, ff + f] + up_offset)
 __global__ void glu_act_rows_kernel(float *__restrict__ h, const float *__restrict__ gu, int ff, int act, float alpha, float limit, float up_offset) {
 	const int m = blockIdx.y;
@@ -603,6 +522,28 @@ __global__ void __launch_bounds__(128) moe_down_slots_kernel(float *__restrict__
 	float v = warp_dot<DT>(wd, ((size_t)e * dim + n) * ff, h + (size_t)s * ff, ff, vec);
 	if (out_scale) v *= wts[s];
 	if ((threadIdx.x & 31) == 0) y[(size_t)s * ldy + n] = v;
+}
+
+// ---- experts, rows grouped by expert (prompt portions on the tensor cores) ---------------------------------------------------
+// order[j]: the slot (row * top + k) that sits at place j once the slots are sorted by expert.  out16[j, :] = the slot's row
+// of x, times the slot's weight when the weight multiplies the expert's input, rounded to the 16-bit operand type.
+template <typename T>
+__global__ void moe_gather_rows_kernel(T *__restrict__ out, const float *__restrict__ x, int ldx, const int *__restrict__ order,
+                                       const float *__restrict__ wts, int top, int K, int in_scale) {
+	const int s = order[blockIdx.x];
+	const float w = in_scale ? wts[s] : 1.f;
+	const float *row = x + (size_t)(s / top) * ldx;
+	T *dst = out + (size_t)blockIdx.x * K;
+	for (int e = threadIdx.x; e < K; e += blockDim.x) dst[e] = T(row[e] * w);
+}
+// y[order[j], :] = ys[j, :] (times the slot's weight when it multiplies the expert's output): back to slot order
+__global__ void moe_scatter_rows_kernel(float *__restrict__ y, int ldy, const float *__restrict__ ys, int lds, const int *__restrict__ order,
+                                        const float *__restrict__ wts, int dim, int out_scale) {
+	const int s = order[blockIdx.x];
+	const float w = out_scale ? wts[s] : 1.f;
+	const float *src = ys + (size_t)blockIdx.x * lds;
+	float *dst = y + (size_t)s * ldy;
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) dst[e] = src[e] * w;
 }
 
 } // namespace stack
@@ -780,5 +721,20 @@ extern "C" int yalm_moe_down_slots(float *y, int ldy, const float *h, const void
 	if (!y || !h || !wd || !ids || !wts || n < 1 || top < 1) return YALM_EINVAL;
 	const bool vec = row_vec(wd, ff, dtype) && aligned16(h) && ff % 4 == 0;
 	DISPATCH_DT(dtype, (moe_down_slots_kernel<DT><<<dim3((dim + 3) / 4, n * top), 128, 0, (cudaStream_t)s>>>(y, ldy, h, wd, ids, wts, ff, dim, out_scale, vec)));
+	return (int)cudaGetLastError();
+}
+
+// Slots sorted by expert (order[j] = slot at place j): the A operand of the per-expert tensor-core products, and the way back.
+extern "C" int yalm_moe_gather_rows16(void *out16, const float *x, int ldx, const int *order, const float *wts, int n_slots, int top, int dim,
+                                      int bf16, int in_scale, yalm_stream_t s) {
+	if (!out16 || !x || !order || !wts || n_slots < 1 || top < 1 || dim < 1) return YALM_EINVAL;
+	if (bf16) moe_gather_rows_kernel<__nv_bfloat16><<<n_slots, 256, 0, (cudaStream_t)s>>>(static_cast<__nv_bfloat16 *>(out16), x, ldx, order, wts, top, dim, in_scale);
+	else moe_gather_rows_kernel<__half><<<n_slots, 256, 0, (cudaStream_t)s>>>(static_cast<__half *>(out16), x, ldx, order, wts, top, dim, in_scale);
+	return (int)cudaGetLastError();
+}
+extern "C" int yalm_moe_scatter_rows(float *y, int ldy, const float *ys, int lds, const int *order, const float *wts, int n_slots, int dim,
+                                     int out_scale, yalm_stream_t s) {
+	if (!y || !ys || !order || !wts || n_slots < 1 || dim < 1) return YALM_EINVAL;
+	moe_scatter_rows_kernel<<<n_slots, 256, 0, (cudaStream_t)s>>>(y, ldy, ys, lds, order, wts, dim, out_scale);
 	return (int)cudaGetLastError();
 }

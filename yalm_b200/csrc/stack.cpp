@@ -172,6 +172,9 @@ struct Model::StackScratch {
 	void *a16 = nullptr;
 	float *attn_ws = nullptr; // split partials of decode-sized attention calls
 	int *ids = nullptr, *tokens = nullptr, *want = nullptr, *targets = nullptr;
+	float *moe_gu = nullptr, *moe_ys = nullptr; // experts on the tensor cores: (gate | up) and down outputs of the slots sorted by expert
+	int *order = nullptr;                       // slot at every place of that order
+	unsigned *ticket = nullptr; // arrival counter of the one-row products with a fused tail (zero between launches)
 	std::vector<Placement> placements; // filled by build_stack, consumed by cuda_stack
 	~StackScratch() { cudaFree(arena); }
 };
@@ -307,6 +310,7 @@ void Model::cuda_stack(int device) {
 	const size_t cap = S.cap, W = s.width, top = std::max(1, s.max_top()), ff = std::max(1, s.max_ff());
 	const size_t nqkv = (size_t)s.max_q_dim() + s.max_kv_dim() + s.max_v_dim();
 	const size_t kmax = std::max({W, (size_t)s.max_o_dim(), ff});
+	const bool moe = s.max_experts() > 0 && c.weight_dtype != DType::F32; // the grouped route needs 16-bit operands
 	auto pad = [](size_t b) { return (b + 255) / 256 * 256; };
 	struct Slot {
 		void **p;
@@ -317,13 +321,14 @@ void Model::cuda_stack(int device) {
 	             {(void **)&S.xn, 4 * cap * W},          {(void **)&S.logits, 4 * cap * (size_t)s.vocab}, {(void **)&S.probs, 4 * cap},
 	             {(void **)&S.a16, 2 * cap * top * kmax}, {(void **)&S.ids, 4 * cap * top},       {(void **)&S.tokens, 4 * cap},
 	             {(void **)&S.want, 4 * cap},            {(void **)&S.targets, 4 * cap},
-	             {(void **)&S.attn_ws, 4 * yalm_attn_window_pool_workspace(256)}};
+	             {(void **)&S.attn_ws, 4 * yalm_attn_window_pool_workspace(256)}, {(void **)&S.ticket, 256},
+	             {(void **)&S.moe_gu, moe ? 4 * cap * top * 2 * ff : 0}, {(void **)&S.moe_ys, moe ? 4 * cap * top * W : 0}, {(void **)&S.order, 4 * cap * top}};
 	size_t total = 0;
 	for (auto &sl : slots) total += pad(sl.bytes);
 	if (cudaMalloc((void **)&S.arena, total) != cudaSuccess) die("device allocation failed (pass scratch)");
 	cudaMemset(S.arena, 0, total);
 	char *p = S.arena;
-	for (auto &sl : slots) *sl.p = p, p += pad(sl.bytes);
+	for (auto &sl : slots) *sl.p = sl.bytes ? p : nullptr, p += pad(sl.bytes);
 	if (cudaDeviceSynchronize() != cudaSuccess) die("device error after upload");
 }
 
@@ -346,9 +351,65 @@ static int stack_linear(Model &, const Config &c, void *a16, float *y, int ldy, 
 	return yalm_linear_rows(y, ldy, x, ldx, w, dt, M, N, K, alpha, st);
 }
 
+// One row, 16-bit or fp32 weights with 16-byte rows: the product and what follows it run as one launch (ops_stack_gemv.cu).
+// YALM_STACK_FUSE=0: A/B against the separate kernels.
+static bool gemv_fusable(const Config &c, int n, int K, const void *w, const void *x) {
+	static const bool off = [] { const char *e = getenv("YALM_STACK_FUSE"); return e && e[0] == '0'; }();
+	return !off && n == 1 && K % 8 == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0 && (size_t)K * dtype_size(c.weight_dtype) % 16 == 0;
+}
+
 static bool attn_mma_off() { // YALM_STACK_ATTN_MMA=0: A/B against the SIMT kernel
 	static const bool off = [] { const char *e = getenv("YALM_STACK_ATTN_MMA"); return e && e[0] == '0'; }();
 	return off;
+}
+
+// Experts of a prompt portion on the tensor cores: the (row, expert) slots are sorted by expert on the host (one small copy
+// of the chosen ids), each expert's rows are gathered into one 16-bit operand (scaled by the slot's weight when the weight
+// multiplies the expert's input), and gate, up and down run as one tcgen05 product per expert that has rows; the down
+// outputs go back to slot order, where the output norm sums a row's slots.  Same arithmetic as the slot kernels up to the
+// rounding of the operands.
+static bool moe_grouped_off() { // YALM_STACK_MOE_TC=0: A/B against the slot kernels
+	static const bool off = [] { const char *e = getenv("YALM_STACK_MOE_TC"); return e && e[0] == '0'; }();
+	return off;
+}
+
+int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, int n, int act, cudaStream_t st) {
+	const Config &c = *config;
+	const FfnSpec &f = L.spec.ffn;
+	const int W = c.stack->width, ff = f.ff, top = f.top, E = f.experts, ns = n * top, bf16 = c.weight_dtype == DType::BF16;
+	std::vector<int> ids(ns), order(ns), start(E + 1, 0);
+	ST_TRY(cudaMemcpyAsync(ids.data(), S.ids, sizeof(int) * ns, cudaMemcpyDeviceToHost, st));
+	ST_TRY(cudaStreamSynchronize(st));
+	for (int s = 0; s < ns; ++s) {
+		if (ids[s] < 0 || ids[s] >= E) return YALM_EINVAL;
+		++start[ids[s] + 1];
+	}
+	for (int e = 0; e < E; ++e) start[e + 1] += start[e];
+	{
+		std::vector<int> at(start.begin(), start.end() - 1);
+		for (int s = 0; s < ns; ++s) order[at[ids[s]]++] = s; // stable: slots of an expert stay in row order
+	}
+	ST_TRY(cudaMemcpyAsync(S.order, order.data(), sizeof(int) * ns, cudaMemcpyHostToDevice, st));
+	ST_TRY(yalm_moe_gather_rows16(S.a16, S.x, W, S.order, S.wts, ns, top, W, bf16, f.weight_on_input ? 1 : 0, st));
+	const size_t es = dtype_size(c.weight_dtype);
+	for (int e = 0; e < E; ++e) {
+		const int m = start[e + 1] - start[e];
+		if (!m) continue;
+		const char *a = static_cast<const char *>(S.a16) + (size_t)start[e] * W * 2;
+		float *gu = S.moe_gu + (size_t)start[e] * 2 * ff;
+		ST_TRY(yalm_gemm_16(gu, 2 * ff, a, static_cast<const char *>(L.wg) + (size_t)e * ff * W * es, m, ff, W, 0, bf16, 1.f, st));
+		ST_TRY(yalm_gemm_16(gu + ff, 2 * ff, a, static_cast<const char *>(L.wu) + (size_t)e * ff * W * es, m, ff, W, 0, bf16, 1.f, st));
+	}
+	ST_TRY(yalm_glu_act_rows(S.h, S.moe_gu, ns, ff, act, f.act_alpha, f.limit, f.up_offset, st));
+	ST_TRY(yalm_cast_rows16(S.a16, S.h, ff, ns, ff, bf16, st));
+	for (int e = 0; e < E; ++e) {
+		const int m = start[e + 1] - start[e];
+		if (!m) continue;
+		ST_TRY(yalm_gemm_16(S.moe_ys + (size_t)start[e] * W, W, static_cast<const char *>(S.a16) + (size_t)start[e] * ff * 2,
+		                    static_cast<const char *>(L.wdown) + (size_t)e * W * ff * es, m, W, ff, 0, bf16, 1.f, st));
+	}
+	ST_TRY(yalm_moe_scatter_rows(S.y, W, S.moe_ys, W, S.order, S.wts, ns, W, f.weight_on_input ? 0 : 1, st));
+	return (int)cudaGetLastError(); // `order` was pageable host memory: the copy call returned after staging it
 }
 
 int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want) {
@@ -365,11 +426,16 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 		const yalm::MixerSpec &m = L.spec.mix;
 		const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, no = m.heads * m.vdim, ld = nq + nk + nv;
 		// ---- token mixer ----
-		ST_TRY(stack_linear(*this, c, S.a16, S.qkv, ld, S.x, W, L.wqkv, n, ld, W, 1.f, st));
-		ST_TRY(yalm_qkv_post_rows(S.qkv, ld, L.kring, L.vring, S.vfirst, nv, L.qnorm, L.knorm, L.vmix, L.vmode, n, m.heads, m.kv_heads, m.dim, m.vdim,
-		                          L.ring, sp.norm_eps, f32, pos0, ctl, st));
-		if (m.pool > 0)
-			ST_TRY(yalm_kv_pool_rows(L.kpool, L.vpool, L.kring, L.vring, n, m.kv_heads, m.dim, m.vdim, L.ring, m.pool, L.max_blocks, f32, pos0, ctl, st));
+		if (gemv_fusable(c, n, W, L.wqkv, S.x)) {
+			ST_TRY(yalm_gemv_qkv_post(S.qkv, S.x, L.wqkv, W, dt, L.kring, L.vring, S.vfirst, L.qnorm, L.knorm, L.vmix, L.vmode, m.heads, m.kv_heads, m.dim,
+			                          m.vdim, L.ring, sp.norm_eps, f32, L.kpool, L.vpool, m.pool, L.max_blocks, pos0, ctl, S.ticket, st));
+		} else {
+			ST_TRY(stack_linear(*this, c, S.a16, S.qkv, ld, S.x, W, L.wqkv, n, ld, W, 1.f, st));
+			ST_TRY(yalm_qkv_post_rows(S.qkv, ld, L.kring, L.vring, S.vfirst, nv, L.qnorm, L.knorm, L.vmix, L.vmode, n, m.heads, m.kv_heads, m.dim, m.vdim,
+			                          L.ring, sp.norm_eps, f32, pos0, ctl, st));
+			if (m.pool > 0)
+				ST_TRY(yalm_kv_pool_rows(L.kpool, L.vpool, L.kring, L.vring, n, m.kv_heads, m.dim, m.vdim, L.ring, m.pool, L.max_blocks, f32, pos0, ctl, st));
+		}
 		// many rows over bf16 rings: tensor-core attention; decode-sized calls, the fp32 cache and other head sizes: the SIMT kernel
 		if (!f32 && n >= 16 && ld % 4 == 0 && no % 2 == 0 && yalm_attn_window_pool_mma_shape(m.dim, m.vdim) && !attn_mma_off())
 			ST_TRY(yalm_attn_window_pool_mma(S.att, no, S.qkv, ld, L.kring, L.vring, L.kpool, L.vpool, n, m.heads, m.kv_heads, m.dim, m.vdim, L.ring,
@@ -377,22 +443,35 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 		else
 		ST_TRY(yalm_attn_window_pool(S.att, no, S.qkv, ld, L.kring, L.vring, L.kpool, L.vpool, S.attn_ws, n, m.heads, m.kv_heads, m.dim, m.vdim, L.ring,
 		                             L.max_blocks, m.window, m.pool, m.scale, f32, c.max_seq_len, pos0, ctl, st));
-		ST_TRY(stack_linear(*this, c, S.a16, S.y, W, S.att, no, L.wo, n, W, no, 1.f, st));
-		ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, 1, L.norm1, woff, sp.norm_eps, n, W, st));
+		if (gemv_fusable(c, n, no, L.wo, S.att))
+			ST_TRY(yalm_gemv_norm_residual(S.x, S.y, S.att, L.wo, L.norm1, woff, sp.norm_eps, no, W, dt, 0, 0, 0.f, 0.f, 0.f, S.ticket, st));
+		else {
+			ST_TRY(stack_linear(*this, c, S.a16, S.y, W, S.att, no, L.wo, n, W, no, 1.f, st));
+			ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, 1, L.norm1, woff, sp.norm_eps, n, W, st));
+		}
 		// ---- feed-forward ----
 		const FfnSpec &f = L.spec.ffn;
 		const int act = f.act == yalm::GluAct::SigmoidScaled ? 2 : f.act == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
 		if (f.kind == FfnSpec::Dense) {
 			ST_TRY(stack_linear(*this, c, S.a16, S.gu, 2 * f.ff, S.x, W, L.wgu, n, 2 * f.ff, W, 1.f, st));
-			ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.ff, act, f.act_alpha, f.limit, f.up_offset, st));
-			ST_TRY(stack_linear(*this, c, S.a16, S.y, W, S.h, f.ff, L.wdown, n, W, f.ff, 1.f, st));
-			ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, 1, L.norm2, woff, sp.norm_eps, n, W, st));
+			if (gemv_fusable(c, n, f.ff, L.wdown, S.gu) && (size_t)f.ff * 4 % 16 == 0)
+				ST_TRY(yalm_gemv_norm_residual(S.x, S.y, S.gu, L.wdown, L.norm2, woff, sp.norm_eps, f.ff, W, dt, 1, act, f.act_alpha, f.limit, f.up_offset,
+				                               S.ticket, st));
+			else {
+				ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.ff, act, f.act_alpha, f.limit, f.up_offset, st));
+				ST_TRY(stack_linear(*this, c, S.a16, S.y, W, S.h, f.ff, L.wdown, n, W, f.ff, 1.f, st));
+				ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, 1, L.norm2, woff, sp.norm_eps, n, W, st));
+			}
 		} else if (f.kind == FfnSpec::Moe) {
 			ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.x, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
 			                             f.renormalize ? 1 : 0, st));
-			ST_TRY(yalm_moe_glu_slots(S.h, S.x, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
-			                          f.weight_on_input ? 1 : 0, st));
-			ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
+			if (S.moe_gu && !from_ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
+				ST_TRY(stack_moe_grouped(S, L, n, act, st));
+			else {
+				ST_TRY(yalm_moe_glu_slots(S.h, S.x, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
+				                          f.weight_on_input ? 1 : 0, st));
+				ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
+			}
 			ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, f.top, L.norm2, woff, sp.norm_eps, n, W, st));
 		}
 	}
@@ -521,6 +600,8 @@ int Model::stack_generate(InferenceState &s, int token, int pos, int n_gen, floa
 				const int rc = step();
 				const cudaError_t end = cudaStreamEndCapture(st, &g.graph);
 				if (rc || end != cudaSuccess) return rc ? rc : (int)end;
+				size_t nodes = 0;
+				if (cudaGraphGetNodes(g.graph, nullptr, &nodes) == cudaSuccess) _stack_step_nodes = (int)nodes;
 				ST_TRY(cudaGraphInstantiate(&g.instance, g.graph, 0));
 				g.is_created = true;
 			}

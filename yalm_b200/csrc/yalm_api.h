@@ -325,11 +325,13 @@ private:
 	struct StackScratch;
 	std::shared_ptr<StackScratch> _scratch;
 	int _stack_pos = 0; // next position of the current sequence
+	int _stack_step_nodes = 0; // kernel nodes of the captured decode step (pass + sampler), once a step has been captured
 	void build_stack(YALMData &data);
 	void cuda_stack(int device);
 	int stack_rows(InferenceState &s, const int *tokens, int n, int pos0, const int *want, int n_want, float *logits_out, const int *targets,
 	               float *probs_out);
 	int stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want);
+	int stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, int n, int act, cudaStream_t st);
 	int stack_generate(InferenceState &s, int token, int pos, int n_gen, float temperature, unsigned long long seed, int *tokens_out,
 	                   float *logits_out, float *device_ms);
 	Device _device = Device::CPU;
