@@ -401,6 +401,178 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
 	}
 }
 
+// The same attention for bf16 rings whose key and value sizes are 8, 16, ..., 256: every row is read as 16-byte pieces by
+// dk / 8 (dv / 8) neighbouring lanes, so that one warp instruction fetches whole rows and eight of them are in flight per
+// lane; each lane keeps its 8 channels of the R queries and of the R accumulators in registers.  Scores of a 32-key tile
+// pass through shared memory between the two phases (lane = key for the softmax bookkeeping).  Block means (fp32) are read
+// in the same lane layout as two 16-byte pieces.  Same grid, splits, partials and merge as attn_window_pool_kernel.
+template <int R>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_lanes_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                                                 const __nv_bfloat16 *__restrict__ kc,
+                                                                                 const __nv_bfloat16 *__restrict__ vc, const float *__restrict__ kp,
+                                                                                 const float *__restrict__ vp, float *__restrict__ part, int n_heads,
+                                                                                 int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool,
+                                                                                 float scale, int pos0, const int *__restrict__ ctl) {
+	extern __shared__ __align__(16) float sm[];
+	float *qs = sm;                                    // R x dk
+	float *macc = qs + R * dk;                         // kAttnWarps x R x dv
+	float *mml = macc + kAttnWarps * R * dv;           // kAttnWarps x R x 2
+	float *sc = mml + kAttnWarps * R * 2;              // kAttnWarps x R x 32
+	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
+	const int g = blockIdx.x / hg, h0 = g * rep + (blockIdx.x % hg) * R, nh = min(R, g * rep + rep - h0);
+	const int m = blockIdx.y, z = blockIdx.z, nsplit = gridDim.z;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int i = first_pos(ctl, pos0) + m;
+	const int lo = window > 0 ? max(0, i - window + 1) : 0;
+	const int nb = (window > 0 && pool > 0 && i - window + 1 >= pool) ? (i - window + 1) / pool : 0;
+	for (int e = threadIdx.x; e < R * dk; e += blockDim.x) {
+		const int r = e / dk, d = e % dk;
+		qs[e] = r < nh ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
+	}
+	__syncthreads();
+	const int LK = dk >> 3, LV = dv >> 3;                          // lanes per key / value row
+	const int subk = lane % LK, rgk = lane / LK, rpk = 32 / LK;    // piece of the row, row within a step, rows per step
+	const int subv = lane % LV, rgv = lane / LV, rpv = 32 / LV;
+	float qr[R][8];
+#pragma unroll
+	for (int r = 0; r < R; ++r)
+#pragma unroll
+		for (int j = 0; j < 8; ++j) qr[r][j] = qs[r * dk + subk * 8 + j];
+	const __nv_bfloat16 *kbase = kc + (size_t)g * ring * dk + subk * 8, *vbase = vc + (size_t)g * ring * dv + subv * 8;
+	const float *kpb = kp ? kp + (size_t)g * max_blocks * dk + subk * 8 : nullptr, *vpb = vp ? vp + (size_t)g * max_blocks * dv + subv * 8 : nullptr;
+	float *scw = sc + warp * R * 32;
+	float mx[R], l[R], acc[R][8];
+#pragma unroll
+	for (int r = 0; r < R; ++r) {
+		mx[r] = -INFINITY, l[r] = 0.f;
+#pragma unroll
+		for (int j = 0; j < 8; ++j) acc[r][j] = 0.f;
+	}
+	const int ntok = i - lo + 1, ptiles = (nb + 31) / 32, ntiles = ptiles + (ntok + 31) / 32, per = (ntiles + nsplit - 1) / nsplit;
+	const int t_end = min(ntiles, (z + 1) * per);
+	constexpr int KU = 8; // row steps in flight
+	for (int t = z * per + warp; t < t_end; t += kAttnWarps) {
+		const bool pooled = t < ptiles;
+		const int idx0 = pooled ? t * 32 : (t - ptiles) * 32, cnt = min(32, (pooled ? nb : ntok) - idx0);
+		// ---- scores ----
+		for (int u0 = 0; u0 * rpk < cnt; u0 += KU) {
+			float kf[KU][8];
+			if (pooled) {
+#pragma unroll
+				for (int u = 0; u < KU; ++u) {
+					const float *kr = kpb + (size_t)(idx0 + min((u0 + u) * rpk + rgk, cnt - 1)) * dk;
+					const float4 a = __ldg(reinterpret_cast<const float4 *>(kr)), b = __ldg(reinterpret_cast<const float4 *>(kr + 4));
+					kf[u][0] = a.x, kf[u][1] = a.y, kf[u][2] = a.z, kf[u][3] = a.w, kf[u][4] = b.x, kf[u][5] = b.y, kf[u][6] = b.z, kf[u][7] = b.w;
+				}
+			} else {
+				uint4 w[KU];
+#pragma unroll
+				for (int u = 0; u < KU; ++u)
+					w[u] = __ldg(reinterpret_cast<const uint4 *>(kbase + (size_t)((lo + idx0 + min((u0 + u) * rpk + rgk, cnt - 1)) % ring) * dk));
+#pragma unroll
+				for (int u = 0; u < KU; ++u) Elem<YALM_BF16>::unpack(w[u], kf[u]);
+			}
+#pragma unroll
+			for (int u = 0; u < KU; ++u) {
+				const int row = (u0 + u) * rpk + rgk;
+				float d[R];
+#pragma unroll
+				for (int r = 0; r < R; ++r) {
+					d[r] = 0.f;
+#pragma unroll
+					for (int j = 0; j < 8; ++j) d[r] = fmaf(kf[u][j], qr[r][j], d[r]);
+				}
+				for (int o = LK >> 1; o > 0; o >>= 1)
+#pragma unroll
+					for (int r = 0; r < R; ++r) d[r] += __shfl_xor_sync(kFull, d[r], o);
+				if (subk == 0 && row < 32) {
+#pragma unroll
+					for (int r = 0; r < R; ++r) scw[r * 32 + row] = d[r];
+				}
+			}
+		}
+		__syncwarp();
+		// ---- online softmax, lane = key ----
+#pragma unroll
+		for (int r = 0; r < R; ++r) {
+			const float sv = lane < cnt ? scw[r * 32 + lane] : -INFINITY;
+			const float nmx = fmaxf(mx[r], warp_max(sv)); // finite: the tile holds at least one key
+			const float corr = mx[r] == -INFINITY ? 0.f : expf(mx[r] - nmx);
+			const float pv = lane < cnt ? expf(sv - nmx) : 0.f;
+			l[r] = l[r] * corr + warp_sum(pv);
+			mx[r] = nmx;
+			scw[r * 32 + lane] = pv;
+#pragma unroll
+			for (int j = 0; j < 8; ++j) acc[r][j] *= corr;
+		}
+		__syncwarp();
+		// ---- P V ----
+		for (int u0 = 0; u0 * rpv < cnt; u0 += KU) {
+			float vf[KU][8];
+			if (pooled) {
+#pragma unroll
+				for (int u = 0; u < KU; ++u) {
+					const float *vr = vpb + (size_t)(idx0 + min((u0 + u) * rpv + rgv, cnt - 1)) * dv;
+					const float4 a = __ldg(reinterpret_cast<const float4 *>(vr)), b = __ldg(reinterpret_cast<const float4 *>(vr + 4));
+					vf[u][0] = a.x, vf[u][1] = a.y, vf[u][2] = a.z, vf[u][3] = a.w, vf[u][4] = b.x, vf[u][5] = b.y, vf[u][6] = b.z, vf[u][7] = b.w;
+				}
+			} else {
+				uint4 w[KU];
+#pragma unroll
+				for (int u = 0; u < KU; ++u)
+					w[u] = __ldg(reinterpret_cast<const uint4 *>(vbase + (size_t)((lo + idx0 + min((u0 + u) * rpv + rgv, cnt - 1)) % ring) * dv));
+#pragma unroll
+				for (int u = 0; u < KU; ++u) Elem<YALM_BF16>::unpack(w[u], vf[u]);
+			}
+#pragma unroll
+			for (int u = 0; u < KU; ++u) {
+				const int row = (u0 + u) * rpv + rgv;
+#pragma unroll
+				for (int r = 0; r < R; ++r) {
+					const float pk = row < cnt ? scw[r * 32 + row] : 0.f; // past the end: a repeated row with no weight
+#pragma unroll
+					for (int j = 0; j < 8; ++j) acc[r][j] = fmaf(pk, vf[u][j], acc[r][j]);
+				}
+			}
+		}
+		__syncwarp(); // the next tile's scores overwrite scw
+	}
+	// the row groups of a warp hold partial sums of the same channels
+	for (int o = 16; o >= LV; o >>= 1)
+#pragma unroll
+		for (int r = 0; r < R; ++r)
+#pragma unroll
+			for (int j = 0; j < 8; ++j) acc[r][j] += __shfl_xor_sync(kFull, acc[r][j], o);
+#pragma unroll
+	for (int r = 0; r < R; ++r) {
+		if (rgv == 0) {
+#pragma unroll
+			for (int j = 0; j < 8; ++j) macc[(warp * R + r) * dv + subv * 8 + j] = acc[r][j];
+		}
+		if (lane == 0) mml[(warp * R + r) * 2] = mx[r], mml[(warp * R + r) * 2 + 1] = l[r];
+	}
+	__syncthreads();
+	for (int r = warp; r < nh; r += kAttnWarps) { // one warp finishes one head
+		float M = -INFINITY;
+		for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, mml[(w * R + r) * 2]);
+		float wt[kAttnWarps], L = 0.f;
+		for (int w = 0; w < kAttnWarps; ++w) {
+			const float mw = mml[(w * R + r) * 2];
+			wt[w] = mw == -INFINITY ? 0.f : expf(mw - M);
+			L += wt[w] * mml[(w * R + r) * 2 + 1];
+		}
+		const int h = h0 + r;
+		float *pr = part ? part + ((size_t)(m * n_heads + h) * nsplit + z) * (dv + 2) : nullptr;
+		for (int c = lane; c < dv; c += 32) {
+			float o = 0.f;
+			for (int w = 0; w < kAttnWarps; ++w) o += wt[w] * macc[(w * R + r) * dv + c];
+			if (pr) pr[c] = o;
+			else out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+		}
+		if (pr && lane == 0) pr[dv] = M, pr[dv + 1] = L;
+	}
+}
+
 // out[m, h, :] = sum_z w_z acc_z / sum_z w_z L_z with w_z = exp(M_z - max M), splits taken in order.  grid (heads, rows).
 __global__ void attn_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit) {
 	const int h = blockIdx.x, m = blockIdx.y;
@@ -627,6 +799,25 @@ extern "C" size_t yalm_attn_window_pool_workspace(int dv) {
 	return (size_t)kAttnMaxParts * (dv + 2);
 }
 
+static bool lanes_size(int d) { return d >= 8 && d <= 256 && (d & (d - 1)) == 0; }
+static bool attn_lanes_off() { // YALM_STACK_ATTN_LANES=0: A/B against the lane-per-key kernel
+	static const bool off = [] { const char *e = getenv("YALM_STACK_ATTN_LANES"); return e && e[0] == '0'; }();
+	return off;
+}
+template <int R>
+static int launch_attn_lanes(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, float *ws,
+                             int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool, float scale, int nsplit,
+                             int pos0, const int *ctl, cudaStream_t st) {
+	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
+	const size_t smem = sizeof(float) * ((size_t)R * dk + (size_t)kAttnWarps * R * dv + kAttnWarps * R * 2 + kAttnWarps * R * 32);
+	if (smem > 48 * 1024) return YALM_EINVAL;
+	attn_window_pool_lanes_kernel<R><<<dim3(n_kv * hg, n, nsplit), kAttnWarps * 32, smem, st>>>(
+	    out, ldo, q, ldq, (const __nv_bfloat16 *)kr, (const __nv_bfloat16 *)vr, kp, vp, nsplit > 1 ? ws : nullptr, n_heads, n_kv, dk, dv, ring, max_blocks,
+	    window, pool, scale, pos0, ctl);
+	if (nsplit > 1) attn_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit);
+	return (int)cudaGetLastError();
+}
+
 template <typename CT, int R, int DVC>
 static int launch_attn_wp(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, float *ws,
                           int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool, float scale, int nsplit,
@@ -657,6 +848,14 @@ extern "C" int yalm_attn_window_pool(float *out, int ldo, const float *q, int ld
 		const int most_keys = window > 0 ? window + (pool > 0 ? max_blocks : 0) : (context > 0 ? context : ring);
 		const int tiles = (most_keys + 31) / 32 + 1;
 		nsplit = std::min({(296 + ctas - 1) / ctas, std::max(1, (tiles + kAttnWarps - 1) / kAttnWarps), std::max(1, kAttnMaxParts / (n * n_heads)), 64});
+	}
+	if (!cache_f32 && lanes_size(dk) && lanes_size(dv) && aligned16(key_ring) && aligned16(value_ring) && aligned16(key_pool) && aligned16(value_pool) &&
+	    !attn_lanes_off()) {
+		if (R == 1)
+			return launch_attn_lanes<1>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring, max_blocks,
+			                            window, pool, scale, nsplit, pos0, ctl, st);
+		return launch_attn_lanes<4>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring, max_blocks, window,
+		                            pool, scale, nsplit, pos0, ctl, st);
 	}
 #define ATTN_CASE(CT, R_, DVC_)                                                                                                       \
 	return launch_attn_wp<CT, R_, DVC_>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring, max_blocks, \
