@@ -123,6 +123,20 @@ def test_attention_bf16_cache_means_are_taken_over_the_cached_values():
     close_enough(got, want, 2e-5)
 
 
+@pytest.mark.parametrize("dk,dv,H,G", [(8, 8, 1, 1), (32, 64, 6, 2), (256, 16, 2, 2), (16, 256, 10, 2), (128, 128, 4, 1)])
+@pytest.mark.parametrize("window,pool,chunk", [(10, 4, 1), (33, 8, 3), (64, 1, 1), (0, 0, 2), (40, 32, 15)])
+def test_attention_rows_split_over_lane_groups(dk, dv, H, G, window, pool, chunk):
+    # bf16 rings with power-of-two sizes: dk / 8 lanes share a key row (1 .. 32 lanes), query heads of a kv head go four at a
+    # time (6 / 2 and 10 / 2 leave a partly filled group), short portions split the keys over CTAs and merge them
+    T = 150
+    q, k, v = crafted_qkv(T, H, G, dk, dv, window, pool, seed=dk + 3 * dv + window)
+    want = O.window_pool_attention(q, k, v, window, pool, 0.3, cache_round=O.round_bf16)
+    span = max(window, pool) if window > 0 else T
+    for ring in ({span + chunk - 1, span + chunk + 11} if window > 0 else {T}):
+        got = api.attn_window_pool(q, k, v, H, G, window, pool, 0.3, ring, chunk, cache_f32=False)
+        close_enough(got, want, 3e-5)
+
+
 @pytest.mark.parametrize("dk,dv,H,G,window,pool,chunk", [
     (64, 32, 4, 2, 40, 8, 64), (128, 128, 2, 1, 40, 8, 23), (64, 128, 3, 3, 100, 16, 200), (128, 64, 4, 1, 7, 3, 64),
     (64, 64, 2, 2, 0, 0, 70), (128, 32, 2, 1, 150, 1, 64), (64, 32, 4, 4, 33, 64, 16), (128, 128, 4, 2, 64, 64, 128)])
