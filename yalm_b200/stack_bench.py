@@ -171,9 +171,34 @@ def run(args, base, emit, write_yalm, shm_path, ClockSampler):
             ref["prefill_frac_of_measured_bf16"] = (2.0 * (params - z["vocab"] * z["width"]) + 4.0 * z["layers"] * z["heads"] * z["dim"] * CONTEXT / 2) * \
                 ref["prefill_tok_s"] / 1e12 / tflops
             row["equal_size_yalm"] = ref
-            out.append(row)
             st.close()
             model.close()
+            # ---- the same model on its per-op kernels (one launch per product, as the layered executor has): the like-for-like
+            # reading of the one-row products, which are the same streaming GEMV in both ----
+            os.environ["YALM_B200_MEGA"] = "0"
+            try:
+                write_yalm(path, arch, "fp16")
+                try:
+                    model = api.Model(path, CONTEXT + 256).cuda(0)
+                finally:
+                    os.unlink(path)
+                st = api.InferenceState(model)
+                if cap:
+                    for p in range(0, CONTEXT - 1, cap):
+                        st.forward_batch(ids[p:min(p + cap, CONTEXT - 1)], p)
+                else:
+                    for p in range(CONTEXT - 1):
+                        st.forward(ids[p], p, api.MODE_HYDRATE)
+                st.generate_greedy(ids[-1], CONTEXT - 1, max(3, args.warmup))
+                st.generate_greedy(ids[0], CONTEXT - 1 + max(3, args.warmup), steps)
+                tok_s = steps / (st.device_ms / 1e3)
+                ref["per_op_kernels"] = {"whole_token_kernel": model.uses_megakernel(), "launches_per_token": model.launches(), "decode_tok_s": tok_s,
+                                         "decode_frac_of_measured_hbm": (2 * params + full_kv) * tok_s / 1e9 / hbm}
+                st.close()
+                model.close()
+            finally:
+                del os.environ["YALM_B200_MEGA"]
+            out.append(row)
     clk = clocks.stop()
     first = out[0]["retezen"]
     emit(dict(base, impl="ours", metric="batch-1 decode tok/s (Retezen, first size; all sizes under `sizes`)", value=first["decode_tok_s"], steps=steps,
