@@ -242,10 +242,7 @@ int yalm_moe_scatter_rows(float *y, int ldy, const float *ys, int lds, const int
 /* One-row (decode) products with what follows them fused in, on the streaming GEMV: the CTA that finishes last runs the tail.
  * yalm_gemv_norm_residual: y = W x (d x n), res += rms(y) (w_offset + nw); gu != 0: x is a (gate | up) row of 2 n floats and
  * the input is act(g) (u + up_offset).  yalm_gemv_qkv_post: qkv = W x, then yalm_qkv_post_rows for the row and the block mean
- * if the position completes a block.  counter: a zeroed device word, left zero.  n % 8 == 0 (fp32: 4), 16-byte aligned.
- * yalm_moe_down_norm_residual: one row's yalm_moe_down_slots with yalm_norm_residual_rows over its `top` slots as the tail. */
-int yalm_moe_down_norm_residual(float *res, float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int top,
-                                int ff, int dim, int out_scale, const float *nw, float w_offset, float eps, unsigned *counter, yalm_stream_t s);
+ * if the position completes a block.  counter: a zeroed device word, left zero.  n % 8 == 0 (fp32: 4), 16-byte aligned. */
 int yalm_gemv_norm_residual(float *res, float *y, const float *x, const void *w, const float *nw, float w_offset, float eps, int n, int d,
                             int dtype, int gu, int act, float act_alpha, float limit, float up_offset, unsigned *counter, yalm_stream_t s);
 int yalm_gemv_qkv_post(float *qkv, const float *x, const void *w, int n, int dtype, void *key_ring, void *value_ring, float *vfirst,

@@ -697,34 +697,6 @@ __global__ void __launch_bounds__(128) moe_down_slots_kernel(float *__restrict__
 	if ((threadIdx.x & 31) == 0) y[(size_t)s * ldy + n] = v;
 }
 
-// One row (a decode step): the down projections of the row's `top` slots with the sublayer's output norm + residual add as
-// their tail — the CTA that finishes last (fence, ticket from one counter, fence) sees every slot's output and runs
-// x += rms(sum of the slots) * (offset + w).  grid (ceil(dim / 4), top); ys: dim floats of shared memory.
-template <int DT>
-__global__ void __launch_bounds__(128) moe_down_norm_row_kernel(float *__restrict__ res, float *__restrict__ y, int ldy, const float *__restrict__ h,
-                                                                const void *__restrict__ wd, const int *__restrict__ ids,
-                                                                const float *__restrict__ wts, int top, int ff, int dim, int out_scale, bool vec,
-                                                                const float *__restrict__ nw, float woff, float eps, unsigned *counter) {
-	extern __shared__ float ys[];
-	__shared__ float red[33];
-	__shared__ int is_last;
-	const int s = blockIdx.y, n = blockIdx.x * 4 + (threadIdx.x >> 5);
-	if (n < dim) {
-		const int e = ids[s];
-		float v = warp_dot<DT>(wd, ((size_t)e * dim + n) * ff, h + (size_t)s * ff, ff, vec);
-		if (out_scale) v *= wts[s];
-		if ((threadIdx.x & 31) == 0) y[(size_t)s * ldy + n] = v;
-	}
-	__threadfence();
-	__syncthreads();
-	if (threadIdx.x == 0) is_last = atomicAdd(counter, 1u) == gridDim.x * gridDim.y - 1;
-	__syncthreads();
-	if (!is_last) return;
-	__threadfence();
-	norm_residual_row(res, y, ldy, top, nw, woff, eps, dim, ys, red);
-	if (threadIdx.x == 0) *counter = 0; // ready for the next launch on this stream
-}
-
 // ---- experts, rows grouped by expert (prompt portions on the tensor cores) ---------------------------------------------------
 // order[j]: the slot (row * top + k) that sits at place j once the slots are sorted by expert.  out16[j, :] = the slot's row
 // of x, times the slot's weight when the weight multiplies the expert's input, rounded to the 16-bit operand type.
@@ -955,18 +927,6 @@ extern "C" int yalm_moe_down_slots(float *y, int ldy, const float *h, const void
 	if (!y || !h || !wd || !ids || !wts || n < 1 || top < 1) return YALM_EINVAL;
 	const bool vec = row_vec(wd, ff, dtype) && aligned16(h) && ff % 4 == 0;
 	DISPATCH_DT(dtype, (moe_down_slots_kernel<DT><<<dim3((dim + 3) / 4, n * top), 128, 0, (cudaStream_t)s>>>(y, ldy, h, wd, ids, wts, ff, dim, out_scale, vec)));
-	return (int)cudaGetLastError();
-}
-
-// One row: yalm_moe_down_slots followed by yalm_norm_residual_rows(res, y, ldy, top, ...) as one launch.  counter: a zeroed
-// device word, left zero.
-extern "C" int yalm_moe_down_norm_residual(float *res, float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts,
-                                           int top, int ff, int dim, int out_scale, const float *nw, float w_offset, float eps, unsigned *counter,
-                                           yalm_stream_t s) {
-	if (!res || !y || !h || !wd || !ids || !wts || !nw || !counter || top < 1 || dim < 1 || (size_t)dim * 4 > 40 * 1024) return YALM_EINVAL;
-	const bool vec = row_vec(wd, ff, dtype) && aligned16(h) && ff % 4 == 0;
-	DISPATCH_DT(dtype, (moe_down_norm_row_kernel<DT><<<dim3((dim + 3) / 4, top), 128, sizeof(float) * dim, (cudaStream_t)s>>>(
-	                       res, y, ldy, h, wd, ids, wts, top, ff, dim, out_scale, vec, nw, w_offset, eps, counter)));
 	return (int)cudaGetLastError();
 }
 

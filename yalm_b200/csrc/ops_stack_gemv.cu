@@ -141,6 +141,12 @@ static int launch_tail(const GemvTailArgs &a, int dtype, cudaStream_t st) {
 
 using namespace yalm::stack;
 
+// YALM_STACK_TAIL=0: the same products with what follows them as separate launches (A/B of the last-CTA tails)
+static bool tail_separate() {
+	static const bool off = [] { const char *e = getenv("YALM_STACK_TAIL"); return e && e[0] == '0'; }();
+	return off;
+}
+
 // res (d) += rms(y) * (w_offset + nw), y = W x (d rows, n columns; y is also left in `y`).  gu != 0: x is a (gate | up) row of
 // 2 n floats and the product's input is act(g) * (u + up_offset) (yalm_glu_act_rows's arithmetic).  counter: a zeroed
 // device word that the kernel leaves zero.
@@ -151,6 +157,11 @@ extern "C" int yalm_gemv_norm_residual(float *res, float *y, const float *x, con
 	a.out = y, a.x = x, a.w = (const char *)w, a.n = n, a.d = d, a.alpha = 1.f;
 	a.glu = gu, a.act = act, a.act_alpha = act_alpha, a.limit = limit, a.up_offset = up_offset;
 	a.tail = 1, a.counter = counter, a.res = res, a.nw = nw, a.woff = w_offset, a.eps = eps;
+	if (tail_separate()) {
+		a.tail = 0;
+		const int rc = launch_tail(a, dtype, (cudaStream_t)s);
+		return rc ? rc : yalm_norm_residual_rows(res, y, d, 1, nw, w_offset, eps, 1, d, s);
+	}
 	return launch_tail(a, dtype, (cudaStream_t)s);
 }
 
@@ -167,5 +178,12 @@ extern "C" int yalm_gemv_qkv_post(float *qkv, const float *x, const void *w, int
 	a.tail = 2, a.counter = counter, a.kring = key_ring, a.vring = value_ring, a.vfirst = vfirst, a.kpool = key_pool, a.vpool = value_pool;
 	a.qnorm = qnorm, a.knorm = knorm, a.vmix = vmix, a.vmode = vmode, a.dk = dk, a.dv = dv, a.ring = ring, a.pool = pool, a.max_blocks = max_blocks;
 	a.n_kv = n_kv, a.cache_f32 = cache_f32, a.eps = eps, a.pos0 = pos0, a.ctl = ctl;
+	if (tail_separate()) {
+		a.tail = 0;
+		int rc = launch_tail(a, dtype, (cudaStream_t)s);
+		if (!rc) rc = yalm_qkv_post_rows(qkv, a.d, key_ring, value_ring, vfirst, a.nv, qnorm, knorm, vmix, vmode, 1, n_heads, n_kv, dk, dv, ring, eps, cache_f32, pos0, ctl, s);
+		if (!rc && pool > 0) rc = yalm_kv_pool_rows(key_pool, value_pool, key_ring, value_ring, 1, n_kv, dk, dv, ring, pool, max_blocks, cache_f32, pos0, ctl, s);
+		return rc;
+	}
 	return launch_tail(a, dtype, (cudaStream_t)s);
 }

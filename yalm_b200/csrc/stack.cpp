@@ -358,11 +358,6 @@ static bool gemv_fusable(const Config &c, int n, int K, const void *w, const voi
 	return !off && n == 1 && K % 8 == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0 && (size_t)K * dtype_size(c.weight_dtype) % 16 == 0;
 }
 
-static bool moe_tail_fusable(int width) { // YALM_STACK_FUSE=0: A/B against the separate kernels
-	static const bool off = [] { const char *e = getenv("YALM_STACK_FUSE"); return e && e[0] == '0'; }();
-	return !off && (size_t)width * 4 <= 40 * 1024;
-}
-
 static bool attn_mma_off() { // YALM_STACK_ATTN_MMA=0: A/B against the SIMT kernel
 	static const bool off = [] { const char *e = getenv("YALM_STACK_ATTN_MMA"); return e && e[0] == '0'; }();
 	return off;
@@ -468,7 +463,6 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 				ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, 1, L.norm2, woff, sp.norm_eps, n, W, st));
 			}
 		} else if (f.kind == FfnSpec::Moe) {
-			bool normed = false;
 			ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.x, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
 			                             f.renormalize ? 1 : 0, st));
 			if (S.moe_gu && !from_ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
@@ -476,14 +470,9 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 			else {
 				ST_TRY(yalm_moe_glu_slots(S.h, S.x, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
 				                          f.weight_on_input ? 1 : 0, st));
-				if (n == 1 && moe_tail_fusable(W)) { // one row: the output norm + residual add run as the down projections' tail
-					ST_TRY(yalm_moe_down_norm_residual(S.x, S.y, W, S.h, L.wdown, dt, S.ids, S.wts, f.top, f.ff, W, f.weight_on_input ? 0 : 1, L.norm2, woff,
-					                                   sp.norm_eps, S.ticket, st));
-					normed = true;
-				} else
-					ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
+				ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
 			}
-			if (!normed) ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, f.top, L.norm2, woff, sp.norm_eps, n, W, st));
+			ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, f.top, L.norm2, woff, sp.norm_eps, n, W, st));
 		}
 	}
 	if (n_want > 0) {
