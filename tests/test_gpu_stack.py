@@ -138,7 +138,7 @@ def test_attention_rows_split_over_lane_groups(dk, dv, H, G, window, pool, chunk
 
 
 @pytest.mark.parametrize("dk,dv,H,G,window,pool,chunk", [
-    (64, 32, 4, 2, 40, 8, 64), (128, 128, 2, 1, 40, 8, 23), (64, 128, 3, 3, 100, 16, 200), (128, 64, 4, 1, 7, 3, 64),
+    (64, 32, 4, 2, 44, 4, 64), (128, 128, 2, 1, 36, 6, 23), (64, 128, 3, 3, 100, 16, 200), (128, 64, 4, 1, 7, 3, 64),
     (64, 64, 2, 2, 0, 0, 70), (128, 32, 2, 1, 150, 1, 64), (64, 32, 4, 4, 33, 64, 16), (128, 128, 4, 2, 64, 64, 128)])
 def test_attention_on_the_tensor_cores(dk, dv, H, G, window, pool, chunk):
     # portions of 16 rows and more over bf16 rings take the mma route; same crafted peaks at every edge
@@ -157,6 +157,7 @@ def test_attention_on_the_tensor_cores(dk, dv, H, G, window, pool, chunk):
     ("attention + experts, top 1", [O.attn_layer(mlp=O.moe(ff=33, experts=4, top=1))]),
     ("attention + experts, top = all", [O.attn_layer(mlp=O.moe(ff=16, experts=3, top=3))]),
     ("value blending", [O.attn_layer(mlp=None), O.attn_layer(mlp=None, v_mix=False, window=4, pool=1), O.attn_layer(mlp=None)]),
+    ("value blending that starts at the second layer", [O.attn_layer(mlp=None, v_mix=False), O.attn_layer(mlp=O.dense(ff=24)), O.attn_layer(mlp=None)]),
     ("one head, pool 1", [O.attn_layer(heads=1, kv_heads=1, dim=8, vdim=8, window=3, pool=1, mlp=O.dense(ff=8, limit=0.0))]),
 ])
 def test_each_mechanism(tmp_path, name, layers):
