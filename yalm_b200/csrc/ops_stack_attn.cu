@@ -2,7 +2,8 @@
 // tensor cores.  Same visibility rule and the same single softmax as ops_stack.cu's attn_window_pool_kernel, which remains
 // the route for decode-sized calls, the fp32 cache and other head sizes.
 //
-// grid (ceil(n / 64), heads), 4 warps x 16 query rows.  Key tiles of 64 go through shared memory: first the pooled blocks
+// grid (ceil(n / 64), heads), 4 warps x 16 query rows.  Key tiles of 64 go through shared memory, two buffers deep (cp.async
+// brings tile t + 1 from the rings while tile t is multiplied): first the pooled blocks
 // 0 .. nb(last row) - 1 (fp32 means, rounded to bf16 as they are staged), then the tokens lo(first row) .. last row from
 // their ring slots.  S = Q K^T and O += P V on mma.sync.m16n8k16 (bf16 in, fp32 accumulate); scores, running max and sum,
 // and the weights are fp32, the weights are rounded to bf16 only as the operand of P V.  Per row the mask is an interval
@@ -27,6 +28,10 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 	             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
 	             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 16 bytes global -> shared without passing through registers; valid false: the 16 bytes are zero-filled (src is not read)
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem, bool valid) {
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem), "r"(valid ? 16 : 0) : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
 	const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
 	return *reinterpret_cast<const uint32_t *>(&h);
@@ -42,7 +47,7 @@ __global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__rest
 	constexpr int KS = DK / 16;               // k-steps of Q K^T
 	constexpr int OT = DV / 8;                // 8-wide output tiles of P V
 	extern __shared__ __align__(16) __nv_bfloat16 smb[];
-	__nv_bfloat16 *Qs = smb, *Ks = Qs + 64 * LDK, *Vs = Ks + 64 * LDK;
+	__nv_bfloat16 *Qs = smb, *Kbuf = Qs + 64 * LDK, *Vbuf = Kbuf + 2 * 64 * LDK; // two key and two value tiles: the next one loads while this one is used
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int h = blockIdx.y, g = h / (n_heads / n_kv), i0 = blockIdx.x * 64;
 	const int p0 = ctl ? ctl[CTL_POS] : pos0;
@@ -77,10 +82,13 @@ __global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__rest
 	const int loA = lo_of(iA), loB = lo_of(iB), nbA = nb_of(iA), nbB = nb_of(iB);
 	const int nb_max = nb_of(i_last), lo_min = lo_of(i_first);
 	const int pooled_tiles = (nb_max + 63) / 64, token_tiles = (i_last - lo_min) / 64 + 1;
-	for (int tt = 0; tt < pooled_tiles + token_tiles; ++tt) {
+	const int n_tiles = pooled_tiles + token_tiles;
+	// Tile tt into buffer tt & 1.  Ring slots go global -> shared with cp.async (16 bytes each; rows past the last position are
+	// zero-filled by a source size of 0), pooled means are fp32 and pass through registers to be rounded.
+	auto stage = [&](int tt) {
 		const bool pooled = tt < pooled_tiles;
-		const int base = pooled ? tt * 64 : lo_min + (tt - pooled_tiles) * 64; // index of the tile's first key: block or position
-		__syncthreads(); // the previous tile's reads are done
+		const int base = pooled ? tt * 64 : lo_min + (tt - pooled_tiles) * 64;
+		__nv_bfloat16 *Ks = Kbuf + (tt & 1) * 64 * LDK, *Vs = Vbuf + (tt & 1) * 64 * LDV;
 		if (pooled) {
 			for (int c = threadIdx.x; c < 64 * (DK / 8); c += 128) {
 				const int r = c / (DK / 8), d = (c % (DK / 8)) * 8;
@@ -103,17 +111,28 @@ __global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__rest
 		} else {
 			for (int c = threadIdx.x; c < 64 * (DK / 8); c += 128) {
 				const int r = c / (DK / 8), d = (c % (DK / 8)) * 8;
-				uint4 pk = make_uint4(0, 0, 0, 0);
-				if (base + r <= i_last) pk = *reinterpret_cast<const uint4 *>(kbase + (size_t)((base + r) % ring) * DK + d);
-				*reinterpret_cast<uint4 *>(Ks + r * LDK + d) = pk;
+				const bool in = base + r <= i_last;
+				cp_async16(Ks + r * LDK + d, kbase + (size_t)((in ? base + r : i_last) % ring) * DK + d, in);
 			}
 			for (int c = threadIdx.x; c < 64 * (DV / 8); c += 128) {
 				const int r = c / (DV / 8), d = (c % (DV / 8)) * 8;
-				uint4 pk = make_uint4(0, 0, 0, 0);
-				if (base + r <= i_last) pk = *reinterpret_cast<const uint4 *>(vbase + (size_t)((base + r) % ring) * DV + d);
-				*reinterpret_cast<uint4 *>(Vs + r * LDV + d) = pk;
+				const bool in = base + r <= i_last;
+				cp_async16(Vs + r * LDV + d, vbase + (size_t)((in ? base + r : i_last) % ring) * DV + d, in);
 			}
 		}
+		asm volatile("cp.async.commit_group;" ::: "memory"); // one group per tile, empty for a pooled one
+	};
+	stage(0);
+	for (int tt = 0; tt < n_tiles; ++tt) {
+		const bool pooled = tt < pooled_tiles;
+		const int base = pooled ? tt * 64 : lo_min + (tt - pooled_tiles) * 64; // index of the tile's first key: block or position
+		const __nv_bfloat16 *Ks = Kbuf + (tt & 1) * 64 * LDK, *Vs = Vbuf + (tt & 1) * 64 * LDV;
+		__syncthreads(); // tile tt - 1 is read: its buffer may take tile tt + 1
+		if (tt + 1 < n_tiles) {
+			stage(tt + 1);
+			asm volatile("cp.async.wait_group 1;" ::: "memory"); // all but the group just committed: tile tt has landed
+		} else
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
 		__syncthreads();
 		// ---- S = Q K^T: 8 key tiles of 8 ----
 		float s[8][4];
@@ -189,7 +208,7 @@ __global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__rest
 template <int DK, int DV>
 static int launch_mma(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, int n, int n_heads,
                       int n_kv, int ring, int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, cudaStream_t st) {
-	const size_t smem = sizeof(__nv_bfloat16) * (2 * 64 * (DK + 8) + 64 * (DV + 8));
+	const size_t smem = sizeof(__nv_bfloat16) * (3 * 64 * (DK + 8) + 2 * 64 * (DV + 8)); // Q, two key tiles, two value tiles
 	static bool configured = false;
 	if (!configured && smem > 48 * 1024) {
 		YALM_TRY(cudaFuncSetAttribute(attn_window_pool_mma_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
