@@ -170,6 +170,20 @@ def test_each_mechanism(tmp_path, name, layers):
     close_enough(got, O.forward(cfg, W, toks), F32_TOL)
 
 
+def test_router_logits_that_saturate_the_sigmoid(tmp_path):
+    # large router logits: in fp32 sigmoid(z) is exactly 1 from z ~ 17 on, so ranking the rounded scores would tie experts whose
+    # scores still differ; the oracle ranks in float64, the library by the logits
+    cfg = O.make_config(width=320, vocab=90, layers=[O.attn_layer(heads=6, kv_heads=1, dim=32, vdim=32, window=20, pool=5,
+                                                                   mlp=O.moe(ff=48, experts=6, top=1))])
+    W = O.random_weights(cfg, 21)       # width 320: logits of std ~14; in 33 of the 200 rows the two largest fp32 scores are equal
+    folder = O.write_checkpoint(str(tmp_path / "sat"), cfg, W, "BF16")
+    toks = tokens_for(cfg, 200)
+    m, s = open_model(folder)
+    got = s.forward_rows(toks, 0, range(len(toks)))
+    close(m, s)
+    close_enough(got, O.forward(cfg, O.as_f64(W), toks), F32_TOL)
+
+
 def test_sizes_that_are_not_vector_multiples(tmp_path):
     # width 100 / ff 30 / key size 10: no 16-byte rows anywhere, so every product takes the scalar route, also in bf16
     cfg = O.make_config(width=100, vocab=77, layers=[O.attn_layer(heads=2, kv_heads=1, dim=10, vdim=6, mlp=O.dense(ff=30)),

@@ -644,20 +644,21 @@ __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__
 	}
 	__syncthreads();
 	if (threadIdx.x == 0) {
-		if (score == 1) {
-			for (int e = 0; e < E; ++e) sc[e] = 1.0f / (1.0f + expf(-sc[e]));
-		} else {
-			float mx = -INFINITY, sum = 0.f;
+		// The experts are ranked by their logits: both score functions are monotonic, and in fp32 a saturated sigmoid (or an
+		// underflowed softmax term) would tie experts whose exact scores still differ.  Ties go to the lower index.
+		float mx = -INFINITY, sum = 0.f;
+		if (score != 1) {
 			for (int e = 0; e < E; ++e) mx = fmaxf(mx, sc[e]);
-			for (int e = 0; e < E; ++e) sc[e] = expf(sc[e] - mx), sum += sc[e];
-			for (int e = 0; e < E; ++e) sc[e] /= sum;
+			for (int e = 0; e < E; ++e) sum += expf(sc[e] - mx);
 		}
 		float tot = 0.f;
 		for (int j = 0; j < top; ++j) {
 			int best = -1;
-			float bv = -INFINITY;
+			float bz = -INFINITY;
 			for (int e = 0; e < E; ++e)
-				if (sc[e] > bv) bv = sc[e], best = e;
+				if (sc[e] > bz) bz = sc[e], best = e;
+			if (best < 0) best = 0, bz = sc[0]; // every logit -inf or NaN: keep the indices valid
+			const float bv = score == 1 ? 1.0f / (1.0f + expf(-bz)) : expf(bz - mx) / sum;
 			ids[(size_t)m * top + j] = best, wts[(size_t)m * top + j] = bv;
 			tot += bv;
 			sc[best] = -INFINITY;
