@@ -181,7 +181,7 @@ int yalm_attn_prefill(void *out16, const void *q16, const uint16_t *key_cache, c
  * control block is given.  Key / value rings are head-major (kv head, slot, channel), slot = position % ring, fp32
  * (cache_f32 != 0) or bf16; pooled keys / values are fp32 (kv head, block, channel). */
 int yalm_embed_rows(float *x, const void *table, const void *positions, int dtype, const int *tokens, int n, int dim, int pos0,
-                    const int *ctl, yalm_stream_t s);
+                    const int *ctl, float scale, yalm_stream_t s);
 int yalm_linear_rows(float *y, int ldy, const float *x, int ldx, const void *w, int dtype, int M, int N, int K, float alpha,
                      yalm_stream_t s);
 int yalm_cast_rows16(void *out16, const float *x, int ldx, int M, int K, int bf16, yalm_stream_t s);
@@ -215,15 +215,16 @@ int yalm_attn_window_pool_mma(float *out, int ldo, const float *q, int ldq, cons
 /* x[m] += rms(sum_{j < nsum} y[m * nsum + j]) * (w_offset + w) */
 int yalm_norm_residual_rows(float *x, const float *y, int ldy, int nsum, const float *w, float w_offset, float eps, int n, int dim,
                             yalm_stream_t s);
-int yalm_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, float w_offset, float eps, int n_rows, int dim,
-                          yalm_stream_t s);
+int yalm_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, int scalar_weight, float w_offset, float eps, int n_rows,
+                          int dim, yalm_stream_t s);
 /* h[m, f] = act(g) * (u + up_offset), g = gu[m, f], u = gu[m, ff + f]; limit > 0: g = min(g, limit), u clamped to +-limit.
  * act: YALM_ACT_GELU, YALM_ACT_SILU, 2 = g * sigmoid(alpha g). */
 int yalm_glu_act_rows(float *h, const float *gu, int n, int ff, int act, float alpha, float limit, float up_offset, yalm_stream_t s);
 /* ids / wts (n, top): the experts with the largest scores (score 0: softmax, 1: sigmoid of the fp32 router logits) and
- * their scores, divided by their sum if renorm. */
+ * their scores, divided by their sum + renorm_eps if renorm.  groups > 1: experts form equal groups of neighbours, a group
+ * scores its best expert, and only the keep_groups best groups' experts can be chosen. */
 int yalm_router_topk_rows(int *ids, float *wts, const float *x, int ldx, const void *wr, int dtype, int n, int n_experts, int top, int dim,
-                          int score, int renorm, yalm_stream_t s);
+                          int score, int renorm, float renorm_eps, int groups, int keep_groups, yalm_stream_t s);
 /* Slot s = (row s / top, expert ids[s]) through stacked expert matrices gate / up (E, ff, dim) and down (E, dim, ff);
  * in_scale: the slot's weight multiplies the expert's input; out_scale: its output. */
 int yalm_moe_glu_slots(float *h, const float *x, int ldx, const void *wg, const void *wu, int dtype, const int *ids, const float *wts, int n,
@@ -249,6 +250,50 @@ int yalm_gemv_qkv_post(float *qkv, const float *x, const void *w, int n, int dty
                        const float *qnorm, const float *knorm, const float *vmix, int vmode, int n_heads, int n_kv, int dk, int dv, int ring,
                        float eps, int cache_f32, float *key_pool, float *value_pool, int pool, int max_blocks, int pos0, const int *ctl,
                        unsigned *counter, yalm_stream_t s);
+
+/* ---- layers with per-sequence state besides a key / value ring (csrc/ops_stack_state.cu) ----
+ * A call whose first position is 0 starts a sequence: stored state is taken as zero.  All state is fp32.
+ * yalm_norm_shift_rows: h = rms(x) (w_offset + w), w one number if scalar_weight; hs (optional) = h + (h of the previous
+ * position - h) * shift, the previous h of the call's first row coming from `state` (dim floats), which then takes the
+ * last row's h.  h may alias x only without hs. */
+int yalm_norm_shift_rows(float *h, float *hs, const float *x, const float *w, int scalar_weight, float w_offset, float eps, const float *shift,
+                         float *state, int n, int dim, int pos0, const int *ctl, yalm_stream_t s);
+/* out[m, c] = silu(bias[c] + sum_j w[c, j] in[m - (taps - 1) + j, c]); w (channels, taps) fp32, bias optional; state
+ * (channels, taps - 1): the inputs of the positions just before the call, replaced by the call's last ones. */
+int yalm_conv_act_rows(float *out, int ldo, const float *in, int ldi, const float *w, const float *bias, float *state, int n, int channels,
+                       int taps, int pos0, const int *ctl, yalm_stream_t s);
+/* Linear recurrence over a (D, P) matrix state per head: S <- decay S; u = beta (v - S^T k) if beta, else vscale v;
+ * S <- S + k u^T; out = S^T q (+ skip v).  k, q (n, kv heads D), head h reading kv head h / rep; v, out (n, heads P);
+ * decay (n, heads) or, if decay_per_channel, (n, heads D) acting on rows; vscale, beta (n, heads) or null; skip (heads) or
+ * null; state (heads, P, D).  D <= 256. */
+int yalm_state_scan_rows(float *out, int ldo, const float *k, int ldk, const float *q, int ldq, const float *v, int ldv, const float *decay,
+                         int ldd, int decay_per_channel, const float *vscale, int ldvs, const float *beta, int ldb, const float *skip,
+                         float *state, int n, int heads, int rep, int D, int P, int pos0, const int *ctl, yalm_stream_t s);
+/* dt = softplus(dt + dt_bias[h]) in place, decay = exp(-exp(a_log[h]) dt). */
+int yalm_ssm_prep_rows(float *dt, int lddt, float *decay, int ldd, const float *dt_bias, const float *a_log, int n, int heads, yalm_stream_t s);
+/* In place: q, k unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q also times q_scale; beta = sigmoid(beta);
+ * g[h, i] = exp(-exp(a_log[h]) softplus(g[h, i] + dt_bias[h, i])). */
+int yalm_delta_prep_rows(float *q, float *k, int ldqk, float *beta, int ldb, float *g, int ldg, const float *a_log, const float *dt_bias, int n,
+                         int heads, int kv_heads, int dim, float unit_eps, float q_scale, yalm_stream_t s);
+/* out = rms over each of `parts` equal parts of (y * silu(z)), times w (dim). */
+int yalm_gated_group_norm_rows(float *out, int ldo, const float *y, int ldy, const float *z, int ldz, const float *w, int n, int dim, int parts,
+                               float eps, yalm_stream_t s);
+/* out[m, h, :] = o[m, h, :] / sqrt(mean o^2 + eps) * w (vdim, shared by heads) * sigmoid(gate[m, h, :]). */
+int yalm_head_norm_gate_rows(float *out, int ldo, const float *o, int ldi, const float *gate, int ldg, const float *w, int n, int heads, int vdim,
+                             float eps, yalm_stream_t s);
+/* q += qb, k += kb in place (null: none); k rows appended to the ring (kv head, slot, channel) and, for positions below
+ * `keep`, to first_buf (kv head, keep, channel). */
+int yalm_qk_bias_append_rows(float *q, float *k, int ld, const float *qb, const float *kb, void *ring_buf, void *first_buf, int n, int n_heads,
+                             int n_kv, int dk, int ring, int keep, int cache_f32, int pos0, const int *ctl, yalm_stream_t s);
+/* Attention with sigmoid weights over keys that are also the values: position i sees j <= i with i - j < window (0: all) or
+ * j < keep; weight = sigmoid(q . k scale + rel[bucket[i - j], h] + hb[h]), not normalised; out *= sigmoid(gate). */
+size_t yalm_attn_sigmoid_workspace(int dk);
+int yalm_attn_sigmoid_rows(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
+                           const float *rel, const int *bucket, const float *hb, float *workspace, int n, int n_heads, int n_kv, int dk, int ring,
+                           int window, int keep, float scale, int cache_f32, int context, int pos0, const int *ctl, yalm_stream_t s);
+/* x[m] += a[m] (+ b[m]) + sum_{j < nsum} y[m * nsum + j]  (a, b, y optional). */
+int yalm_residual_sum_rows(float *x, const float *a, const float *b, const float *y, int ldy, int nsum, int n, int dim, yalm_stream_t s);
+int yalm_softcap_rows(float *z, int n, int dim, float cap, yalm_stream_t s);
 
 /* ---- (3a) host-pointer test entry points (src/infer.cu:890-1007 semantics) ------------------- */
 int yalm_matmul_host(float *xout, const float *x, const void *w, const float *scale, int n, int d, int dtype);
@@ -325,6 +370,9 @@ int yalm_sequence_end(yalm_model *m, yalm_state *s);
 /* Layered models, tests: fp32 copy of layer's key ring (0), value ring (1), pooled keys (2), pooled values (3); and the ring's slot count. */
 int yalm_stack_read(yalm_model *m, int layer, int which, float *dst, size_t count);
 int yalm_stack_ring_slots(const yalm_model *m, int layer);
+/* Layered models, tests: after every layer of the following yalm_forward_rows calls (of at most the portion capacity rows)
+ * the residual rows (n, width) are copied to dst + layer * n * width (host); NULL switches it off. */
+int yalm_stack_tap(yalm_model *m, float *dst);
 /* The same loop with Sampler::sample on the device: temperature 0 = greedy, > 0 = one draw per step with
  * r = uniform(seed, step).  4 bytes per token come back (the reference moves vocab * 4, src/model.cpp:338). */
 int yalm_generate(yalm_model *m, yalm_state *s, int token, int pos, int n_gen, float temperature,

@@ -36,7 +36,9 @@ SYMBOLS = [
     "yalm_model_batch_capacity", "yalm_forward_batch", "yalm_generate", "yalm_state_debug_set_launch_seq", "yalm_tokenize", "yalm_detokenize",
     "yalm_embed_rows", "yalm_linear_rows", "yalm_cast_rows16", "yalm_gemm_16", "yalm_qkv_post_rows", "yalm_kv_pool_rows", "yalm_attn_window_pool",
     "yalm_norm_residual_rows", "yalm_norm_gather_rows", "yalm_glu_act_rows", "yalm_router_topk_rows", "yalm_moe_glu_slots", "yalm_moe_down_slots", "yalm_moe_gather_rows16", "yalm_moe_scatter_rows",
-    "yalm_model_open_dir", "yalm_model_is_stack", "yalm_forward_rows", "yalm_sequence_end", "yalm_stack_read", "yalm_stack_ring_slots", "yalm_attn_window_pool_host", "yalm_gemv_scaled", "yalm_gemv_norm_residual", "yalm_gemv_qkv_post", "yalm_attn_window_pool_mma", "yalm_attn_window_pool_mma_shape", "yalm_attn_window_pool_workspace",
+    "yalm_model_open_dir", "yalm_model_is_stack", "yalm_forward_rows", "yalm_sequence_end", "yalm_stack_read", "yalm_stack_ring_slots", "yalm_stack_tap",
+    "yalm_norm_shift_rows", "yalm_conv_act_rows", "yalm_state_scan_rows", "yalm_ssm_prep_rows", "yalm_delta_prep_rows", "yalm_gated_group_norm_rows",
+    "yalm_head_norm_gate_rows", "yalm_qk_bias_append_rows", "yalm_attn_sigmoid_rows", "yalm_attn_sigmoid_workspace", "yalm_residual_sum_rows", "yalm_softcap_rows", "yalm_attn_window_pool_host", "yalm_gemv_scaled", "yalm_gemv_norm_residual", "yalm_gemv_qkv_post", "yalm_attn_window_pool_mma", "yalm_attn_window_pool_mma_shape", "yalm_attn_window_pool_workspace",
     "yalm_tp_unique_id", "yalm_tp_init", "yalm_tp_finalize", "yalm_tp_shard_plan", "yalm_mega_tile_plan", "yalm_mega_attn_split", "yalm_mega_mma_plan", "yalm_mega_hb_share", "yalm_error_string", "yalm_version",
 ]
 
@@ -74,6 +76,7 @@ def lib():
     L.yalm_sequence_end.argtypes = [vp, vp]
     L.yalm_stack_read.argtypes = [vp, i, i, vp, sz]
     L.yalm_stack_ring_slots.argtypes = [vp, i]
+    L.yalm_stack_tap.argtypes = [vp, vp]
     L.yalm_attn_window_pool_host.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, i, i]
     L.yalm_model_cuda.argtypes = [vp, i, i, i]
     L.yalm_model_close.argtypes = [vp]
@@ -289,6 +292,11 @@ class Model:
         out = np.empty(count, np.float32)
         _check(lib().yalm_stack_read(self.h, layer, which, _p(out), count), "stack_read")
         return out
+
+    def stack_tap(self, buf):
+        """Layered models, tests: the following forward_rows calls copy the residual rows after every layer into `buf`
+        (float32, n_layers * rows * width; the caller keeps it alive); None switches it off."""
+        _check(lib().yalm_stack_tap(self.h, _p(buf) if buf is not None else None), "stack_tap")
 
     def uses_megakernel(self) -> bool:
         return bool(lib().yalm_model_uses_megakernel(self.h))

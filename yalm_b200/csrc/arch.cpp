@@ -151,8 +151,41 @@ int StackSpec::max_v_dim() const {
 }
 int StackSpec::max_o_dim() const {
 	int m = 0;
-	for (const LayerSpec &l : layers) m = std::max(m, l.mix.heads * l.mix.vdim);
+	for (const LayerSpec &l : layers) m = std::max({m, l.mix.heads * l.mix.vdim, l.ssm.inner(), l.delta.heads * l.delta.vdim});
 	return m;
+}
+int StackSpec::max_proj() const {
+	int m = 0;
+	for (const LayerSpec &l : layers) m = std::max(m, l.proj_width());
+	return m;
+}
+int StackSpec::max_conv() const {
+	int m = 0;
+	for (const LayerSpec &l : layers) m = std::max(m, l.conv_width());
+	return m;
+}
+int StackSpec::max_aux() const {
+	int m = 0;
+	for (const LayerSpec &l : layers) m = std::max(m, l.aux_width());
+	return m;
+}
+
+int LayerSpec::proj_width() const {
+	if (kind == MixerKind::StateSpace) return ssm.proj();
+	int n = mix.heads * mix.dim + mix.kv_heads * mix.dim + (mix.values_are_keys ? 0 : mix.kv_heads * mix.vdim) + (mix.out_gate ? mix.heads * mix.vdim : 0);
+	if (kind == MixerKind::Parallel) n += 2 * delta.kv_heads * delta.dim + delta.heads * delta.vdim + delta.heads + delta.decay_rank + delta.gate_rank;
+	return n;
+}
+int LayerSpec::mixed_width() const {
+	if (kind == MixerKind::StateSpace) return ssm.inner();
+	return mix.heads * mix.vdim + (kind == MixerKind::Parallel ? delta.heads * delta.vdim : 0);
+}
+int LayerSpec::conv_width() const {
+	if (kind == MixerKind::StateSpace) return ssm.conv_channels();
+	return kind == MixerKind::Parallel ? 2 * delta.kv_heads * delta.dim + delta.heads * delta.vdim : 0;
+}
+int LayerSpec::aux_width() const {
+	return kind == MixerKind::Parallel ? delta.heads * delta.dim + delta.heads * delta.vdim : 0;
 }
 int StackSpec::max_ff() const {
 	int m = 0;
@@ -200,6 +233,7 @@ std::string retezen_tensor(int layer, TensorRole role, int expert) {
 	case TensorRole::Up: return l + "mlp." + e + "up";
 	case TensorRole::Down: return l + "mlp." + e + "down";
 	case TensorRole::Router: return l + "mlp.router";
+	default: break;
 	}
 	return "";
 }
@@ -285,8 +319,165 @@ int configure_retezen(const JValue &j, Config &cfg) {
 	return 0;
 }
 
+// ---- Fapudra ---------------------------------------------------------------------------------------------------------
+// A decoder-only stack of parallel blocks: x = norm(embed[token] * scale + positions[p]); per layer ONE scalar-weight RMS
+// norm h whose output both sublayers read, x += mixer(shift(h)) + experts(h), where shift blends every coordinate with the
+// previous token's h.  The mixer is either a state-space recurrence or two mixers side by side: a windowed attention with
+// sigmoid weights (values = keys, biased projections, learned distance bias, kept first tokens, output gate) and a gated
+// delta rule with per-channel decay.  Experts: softmax router restricted to the best groups, renormalised weights on
+// the outputs, clamped g * sigmoid(1.702 g) * (u + 1).  Logits pass a tanh soft cap.
+std::string fapudra_tensor(int layer, TensorRole role, int expert) {
+	const std::string l = "l" + std::to_string(layer) + ".", m = l + "mix.", a = m + "left.", d = m + "right.";
+	const std::string e = expert >= 0 ? "e" + std::to_string(expert) + "." : "";
+	switch (role) {
+	case TensorRole::Embed: return "embed";
+	case TensorRole::Positions: return "pos";
+	case TensorRole::EmbedNorm: return "embed.norm";
+	case TensorRole::FinalNorm: return "final.norm";
+	case TensorRole::Head: return "head";
+	case TensorRole::Norm1: return l + "norm1";
+	case TensorRole::Shift: return l + "shift";
+	case TensorRole::Wq: return a + "q";
+	case TensorRole::Wk: return a + "k";
+	case TensorRole::QBias: return a + "q.b";
+	case TensorRole::KBias: return a + "k.b";
+	case TensorRole::RelBias: return a + "rel";
+	case TensorRole::HeadBias: return a + "pb";
+	case TensorRole::OutGate: return a + "g";
+	case TensorRole::Wo: return a + "o";
+	case TensorRole::SsmIn: return m + "in";
+	case TensorRole::SsmConv: return m + "conv";
+	case TensorRole::SsmConvBias: return m + "conv.b";
+	case TensorRole::SsmDtBias: return m + "dt_bias";
+	case TensorRole::SsmALog: return m + "A_log";
+	case TensorRole::SsmD: return m + "D";
+	case TensorRole::SsmNorm: return m + "norm";
+	case TensorRole::SsmOut: return m + "o";
+	case TensorRole::DeltaQ: return d + "q";
+	case TensorRole::DeltaK: return d + "k";
+	case TensorRole::DeltaV: return d + "v";
+	case TensorRole::DeltaQConv: return d + "q.conv";
+	case TensorRole::DeltaKConv: return d + "k.conv";
+	case TensorRole::DeltaVConv: return d + "v.conv";
+	case TensorRole::DeltaBeta: return d + "b";
+	case TensorRole::DeltaALog: return d + "A_log";
+	case TensorRole::DeltaNorm: return d + "norm";
+	case TensorRole::DeltaDecay1: return d + "a1";
+	case TensorRole::DeltaDecay2: return d + "a2";
+	case TensorRole::DeltaDtBias: return d + "dt_bias";
+	case TensorRole::DeltaGate1: return d + "g1";
+	case TensorRole::DeltaGate2: return d + "g2";
+	case TensorRole::DeltaOut: return d + "o";
+	case TensorRole::Gate: return l + "mlp." + e + "gate";
+	case TensorRole::Up: return l + "mlp." + e + "up";
+	case TensorRole::Down: return l + "mlp." + e + "down";
+	case TensorRole::Router: return l + "mlp.router";
+	default: break;
+	}
+	return "";
+}
+
+int fail_fapudra(const char *what) {
+	fprintf(stderr, "yalm_b200: Fapudra config.json: %s\n", what);
+	return YALM_EFORMAT;
+}
+
+int configure_fapudra(const JValue &j, Config &cfg) {
+	auto spec = std::make_shared<StackSpec>();
+	StackSpec &s = *spec;
+	s.arch = "Fapudra";
+	s.width = j["width"].integer(0);
+	s.vocab = j["vocab"].integer(0);
+	s.max_positions = j["max_positions"].integer(0);
+	s.norm_eps = (float)j["norm"]["eps"].number(1e-5);
+	s.embed_scale = (float)j["embedding"]["scale"].number(1.0);
+	s.logit_softcap = (float)j["logit_softcap"].number(0.0);
+	s.learned_positions = true;
+	s.embed_norm = true;
+	s.norm_scalar = true;
+	s.parallel_block = true;
+	s.token_shift = true;
+	s.tensor_name = fapudra_tensor;
+	if (s.width < 1 || s.vocab < 1 || s.max_positions < 1) return fail_fapudra("width, vocab and max_positions must be positive");
+	const JValue &layers = j["layers"];
+	if (!layers.is_array() || layers.arr.empty()) return fail_fapudra("'layers' must be a non-empty list");
+	for (const JValue &jl : layers.arr) {
+		LayerSpec L;
+		const std::string type = jl["type"].string_or("");
+		const JValue &m = jl["mixer"];
+		if (type == "mamba2") {
+			L.kind = MixerKind::StateSpace;
+			SsmSpec &q = L.ssm;
+			q.heads = m["heads"].integer(0), q.vdim = m["vdim"].integer(0), q.state = m["state"].integer(0);
+			q.groups = m["groups"].integer(1), q.norm_groups = m["norm_groups"].integer(1), q.conv = m["conv"].integer(0);
+			if (q.heads < 1 || q.vdim < 1 || q.state < 1 || q.groups < 1 || q.heads % q.groups || q.norm_groups < 1 || q.inner() % q.norm_groups ||
+			    q.conv < 1)
+				return fail_fapudra("bad mamba2 sizes");
+		} else if (type == "parallel") {
+			L.kind = MixerKind::Parallel;
+			const JValue &a = m["left"], &d = m["right"];
+			MixerSpec &x = L.mix;
+			x.heads = a["heads"].integer(0), x.kv_heads = a["kv_heads"].integer(x.heads);
+			x.dim = a["dim"].integer(0), x.vdim = a["vdim"].integer(x.dim);
+			x.scale = (float)a["scale"].number(1.0);
+			x.window = a["mask"]["size"].integer(0), x.keep_first = a["mask"]["keep_first"].integer(0);
+			x.weights = AttnWeights::Sigmoid;
+			x.values_are_keys = x.qk_bias = x.out_gate = true;
+			x.rel_far = a["bias_max"].integer(0);
+			x.rel_rows = 1; // the table's own row count is read from the checkpoint
+			if (x.heads < 1 || x.kv_heads < 1 || x.heads % x.kv_heads || x.dim < 1 || x.window < 0 || x.keep_first < 0)
+				return fail_fapudra("bad attention sizes");
+			if (x.vdim != x.dim) return fail_fapudra("the attention's values are its keys: vdim must equal dim");
+			DeltaSpec &y = L.delta;
+			y.heads = d["heads"].integer(0), y.kv_heads = d["kv_heads"].integer(y.heads);
+			y.dim = d["dim"].integer(0), y.vdim = d["vdim"].integer(y.dim), y.conv = d["conv"].integer(0);
+			if (y.heads < 1 || y.kv_heads < 1 || y.heads % y.kv_heads || y.dim < 1 || y.vdim < 1 || y.conv < 1) return fail_fapudra("bad delta-rule sizes");
+			L.left_scale = (float)m["left_scale"].number(1.0), L.right_scale = (float)m["right_scale"].number(1.0);
+		} else
+			return fail_fapudra("unknown layer type (this build has: mamba2, parallel)");
+		const JValue &f = jl["mlp"];
+		if (f.is_object()) {
+			if (f["kind"].string_or("") != "moe") return fail_fapudra("unknown mlp kind (this build has: moe)");
+			FfnSpec &F = L.ffn;
+			F.kind = FfnSpec::Moe;
+			F.ff = f["expert"]["ff"].integer(0);
+			F.act = GluAct::SigmoidScaled, F.act_alpha = 1.702f, F.up_offset = 1.f;
+			F.limit = (float)f["expert"]["limit"].number(0.0);
+			F.experts = f["router"]["experts"].integer(0), F.top = f["router"]["top"].integer(0);
+			F.groups = f["router"]["groups"]["count"].integer(1), F.keep_groups = f["router"]["groups"]["keep"].integer(F.groups);
+			F.score = RouterScore::Softmax;
+			F.renormalize = true, F.renorm_eps = 1e-20f;
+			F.weight_on_input = false;
+			if (F.ff < 1 || F.experts < 1 || F.top < 1 || F.top > F.experts || F.groups < 1 || F.experts % F.groups || F.keep_groups < 1 ||
+			    F.keep_groups > F.groups || F.top > F.keep_groups * (F.experts / F.groups))
+				return fail_fapudra("bad router sizes");
+		}
+		s.layers.push_back(L);
+	}
+	cfg.stack = spec;
+	cfg.dim = s.width;
+	cfg.vocab_size = s.vocab;
+	cfg.n_layers = (int)s.layers.size();
+	cfg.max_seq_len = s.max_positions;
+	cfg.norm_eps = s.norm_eps;
+	cfg.hidden_dim = std::max(1, s.max_ff());
+	// summary fields: the first attention's head counts if there is one, and a head size that covers every mixer's width
+	cfg.n_heads = cfg.n_kv_heads = 1;
+	for (const LayerSpec &l : s.layers)
+		if (l.kind == MixerKind::Parallel) {
+			cfg.n_heads = l.mix.heads, cfg.n_kv_heads = l.mix.kv_heads;
+			break;
+		}
+	cfg.head_dim = 8;
+	while (cfg.n_heads * cfg.head_dim < std::max(s.max_q_dim(), s.max_o_dim())) cfg.head_dim *= 2;
+	cfg.rotary_dim = 0;
+	cfg.n_experts = s.max_experts(), cfg.n_experts_active = s.max_top();
+	return 0;
+}
+
 const ArchEntry kArchs[] = {
     {"Retezen", configure_retezen},
+    {"Fapudra", configure_fapudra},
 };
 
 } // namespace

@@ -21,6 +21,14 @@ enum class QkNorm { None, WholeProjection /* RMS over all heads' channels at onc
 enum class GluAct { Silu, Gelu, SigmoidScaled /* g * sigmoid(alpha * g) */ };
 // How router logits become expert scores.
 enum class RouterScore { Softmax, Sigmoid };
+// What a layer's token mixer is.
+enum class MixerKind {
+	Attention,  // MixerSpec alone
+	StateSpace, // SsmSpec: a selective state-space recurrence with a scalar decay per head
+	Parallel    // two mixers side by side on the same input, added with fixed scales: attention (MixerSpec) + gated delta rule (DeltaSpec)
+};
+// How attention scores become weights.
+enum class AttnWeights { Softmax, Sigmoid /* sigmoid(score + head bias), not normalised over the keys */ };
 
 struct MixerSpec {
 	int heads = 0, kv_heads = 0; // query head h reads key/value head h / (heads / kv_heads)
@@ -30,6 +38,32 @@ struct MixerSpec {
 	int pool = 0;                // > 0: beside the window, one mean key/value per block of `pool` tokens lying wholly before it
 	QkNorm qk_norm = QkNorm::None;
 	bool v_mix = false;          // values blended with the first v_mix layer's values of the same token
+	int keep_first = 0;          // with a window: the sequence's first keep_first tokens stay visible at their true positions
+	AttnWeights weights = AttnWeights::Softmax;
+	bool values_are_keys = false; // no value projection: v = k as projected (vdim == dim)
+	bool qk_bias = false;        // biases on the q and k projections
+	bool out_gate = false;       // heads * sigmoid(Wg input) before the output projection
+	int rel_rows = 0;            // > 0: a learned bias per (distance bucket, head) is added to the scaled score: distances below
+	int rel_far = 0;             // rel_rows / 2 have a row each, the rest are spaced logarithmically up to rel_far, then the last row
+};
+
+// Selective state-space mixer (state-space duality form): per head a (state, vdim) matrix S,
+// S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, after one projection [z | x | B | C | dt] and a short causal
+// convolution + SiLU over x, B, C; y * silu(z) is RMS-normed in norm_groups parts.
+struct SsmSpec {
+	int heads = 0, vdim = 0, state = 0, groups = 0, norm_groups = 1, conv = 0;
+	int inner() const { return heads * vdim; }
+	int conv_channels() const { return heads * vdim + 2 * groups * state; }
+	int proj() const { return 2 * heads * vdim + 2 * groups * state + heads; }
+};
+
+// Gated delta rule with one decay per head and key channel: per head a (dim, vdim) matrix S,
+// S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  q, k (kv_heads x dim) and v (heads x vdim) pass a
+// short causal convolution + SiLU; q, k are unit vectors per head; the decay and the output gate come from two-stage
+// (low-rank) projections whose inner sizes are the checkpoint's.
+struct DeltaSpec {
+	int heads = 0, kv_heads = 0, dim = 0, vdim = 0, conv = 0;
+	int decay_rank = 0, gate_rank = 0; // filled from the tensors' shapes at load
 };
 
 struct FfnSpec {
@@ -42,15 +76,33 @@ struct FfnSpec {
 	int experts = 0, top = 0;
 	RouterScore score = RouterScore::Softmax;
 	bool renormalize = false;    // selected scores divided by their sum
+	float renorm_eps = 0.f;      // ... plus this
+	int groups = 1, keep_groups = 1; // experts form `groups` equal groups of neighbours; a group scores its best expert and only
+	                             // the keep_groups best groups' experts can be chosen
 	bool weight_on_input = false; // expert(w * h) instead of w * expert(h)
 };
 
 struct LayerSpec {
+	MixerKind kind = MixerKind::Attention;
 	MixerSpec mix;
+	SsmSpec ssm;
+	DeltaSpec delta;
+	float left_scale = 1.f, right_scale = 1.f; // Parallel: left_scale * attention + right_scale * delta rule
 	FfnSpec ffn;
+	// widths of what the layer computes per row, for scratch sizing
+	int proj_width() const;    // the packed input projection
+	int mixed_width() const;   // the input of the output projection(s), summed over the mixers
+	int conv_width() const;    // channels that pass a short convolution
+	int aux_width() const;     // second-stage projections
 };
 
-enum class TensorRole { Embed, Positions, FinalNorm, Head, Norm1, Norm2, Wq, Wk, Wv, Wo, QNorm, KNorm, VMix, Gate, Up, Down, Router };
+enum class TensorRole {
+	Embed, Positions, FinalNorm, Head, Norm1, Norm2, Wq, Wk, Wv, Wo, QNorm, KNorm, VMix, Gate, Up, Down, Router,
+	EmbedNorm, Shift, QBias, KBias, RelBias, HeadBias, OutGate,
+	SsmIn, SsmConv, SsmConvBias, SsmDtBias, SsmALog, SsmD, SsmNorm, SsmOut,
+	DeltaQ, DeltaK, DeltaV, DeltaQConv, DeltaKConv, DeltaVConv, DeltaBeta, DeltaALog, DeltaNorm, DeltaDecay1, DeltaDecay2, DeltaDtBias,
+	DeltaGate1, DeltaGate2, DeltaOut
+};
 
 struct StackSpec {
 	std::string arch;
@@ -61,13 +113,22 @@ struct StackSpec {
 	bool norm_on_output = false;   // x += norm(sublayer(x)) with the sublayer reading x itself, instead of x += sublayer(norm(x))
 	bool learned_positions = false; // x = embed[token] + positions[p]
 	float logit_scale = 1.f;
+	float embed_scale = 1.f;       // x = embed[token] * embed_scale (+ positions[p])
+	bool embed_norm = false;       // ... then the model's norm with its own weight
+	bool norm_scalar = false;      // a norm's weight is one number for all coordinates
+	bool parallel_block = false;   // one norm per layer, mixer and feed-forward both read its output: x += mixer(h) + ff(h)
+	bool token_shift = false;      // the mixer reads h + (previous token's h - h) * shift; the previous h is sequence state
+	float logit_softcap = 0.f;     // > 0: logits <- cap * tanh(logits / cap)
 	// name of a tensor in the checkpoint; `expert` < 0 for tensors that are not per expert
 	std::string (*tensor_name)(int layer, TensorRole role, int expert) = nullptr;
 
 	int max_q_dim() const;  // max over layers of heads * dim
 	int max_kv_dim() const; // kv_heads * dim
 	int max_v_dim() const;  // kv_heads * vdim
-	int max_o_dim() const;  // heads * vdim
+	int max_o_dim() const;  // heads * vdim (every mixer's input of an output projection)
+	int max_proj() const;   // widest packed input projection of a layer
+	int max_conv() const;
+	int max_aux() const;
 	int max_ff() const;
 	int max_top() const;
 	int max_experts() const;

@@ -360,6 +360,12 @@ extern "C" int yalm_stack_read(yalm_model *m, int layer, int which, float *dst, 
 	return m ? m->model->stack_read(layer, which, dst, count) : YALM_EINVAL;
 }
 
+extern "C" int yalm_stack_tap(yalm_model *m, float *dst) {
+	if (!m || !m->model->is_stack()) return YALM_EINVAL;
+	m->model->stack_tap(dst);
+	return 0;
+}
+
 extern "C" int yalm_stack_ring_slots(const yalm_model *m, int layer) {
 	return m ? m->model->stack_ring_slots(layer) : YALM_EINVAL;
 }

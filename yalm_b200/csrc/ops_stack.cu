@@ -67,12 +67,12 @@ __device__ __forceinline__ float warp_dot(const void *w, size_t row_off, const f
 // ---- embedding ---------------------------------------------------------------------------------------------------------
 template <int DT>
 __global__ void embed_rows_kernel(float *__restrict__ x, const void *__restrict__ table, const void *__restrict__ positions,
-                                  const int *__restrict__ tokens, int dim, int pos0, const int *__restrict__ ctl) {
+                                  const int *__restrict__ tokens, int dim, int pos0, const int *__restrict__ ctl, float scale) {
 	const int m = blockIdx.x;
 	const int tok = tokens ? tokens[m] : ctl[CTL_TOKEN];
 	const int p = first_pos(ctl, pos0) + m;
 	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
-		float v = Elem<DT>::get(table, (size_t)tok * dim + e);
+		float v = Elem<DT>::get(table, (size_t)tok * dim + e) * scale;
 		if (positions) v += Elem<DT>::get(positions, (size_t)p * dim + e);
 		x[(size_t)m * dim + e] = v;
 	}
@@ -608,7 +608,7 @@ __global__ void __launch_bounds__(256) norm_residual_rows_kernel(float *__restri
 
 // out[r] = rms(x[rows[r]]) * (offset + w)   (rows null: r itself)
 __global__ void __launch_bounds__(256) norm_gather_rows_kernel(float *__restrict__ out, const float *__restrict__ x, const int *__restrict__ rows,
-                                                               const float *__restrict__ w, float woff, float eps, int dim) {
+                                                               const float *__restrict__ w, int scalar, float woff, float eps, int dim) {
 	__shared__ float red[33];
 	const int r = blockIdx.x, m = rows ? rows[r] : r;
 	const float *src = x + (size_t)m * dim;
@@ -616,7 +616,7 @@ __global__ void __launch_bounds__(256) norm_gather_rows_kernel(float *__restrict
 	for (int e = threadIdx.x; e < dim; e += blockDim.x) ss += src[e] * src[e];
 	ss = block_sum(ss, red);
 	const float s = 1.0f / sqrtf(ss / dim + eps);
-	for (int e = threadIdx.x; e < dim; e += blockDim.x) out[(size_t)r * dim + e] = src[e] * s * (woff + w[e]);
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) out[(size_t)r * dim + e] = src[e] * s * (woff + w[scalar ? 0 : e]);
 }
 
 // ---- gated activation ------------------------------------------------------------------------------------------------
@@ -631,11 +631,14 @@ __global__ void glu_act_rows_kernel(float *__restrict__ h, const float *__restri
 
 // ---- router ----------------------------------------------------------------------------------------------------------
 // z = Wr x (fp32), scores = sigmoid(z) or softmax(z); the `top` largest (ties: the lower index) with their scores as
-// weights, optionally divided by their sum.  One CTA per row; E <= 1024.
+// weights, optionally divided by their sum (+ renorm_eps).  groups > 1: the experts form `groups` equal groups of
+// neighbours, a group scores its best expert, and only experts of the `keep` best groups (ties: the lower index) can be
+// chosen.  One CTA per row; E <= 1024.
 template <int DT>
 __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ x, int ldx,
-                                                               const void *__restrict__ wr, int E, int top, int dim, int score, int renorm, bool vec) {
-	extern __shared__ float sc[]; // E
+                                                               const void *__restrict__ wr, int E, int top, int dim, int score, int renorm,
+                                                               float renorm_eps, int groups, int keep, bool vec) {
+	extern __shared__ float sc[]; // E, then E logits as they were
 	const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const float *xr = x + (size_t)m * ldx;
 	for (int e = warp; e < E; e += 4) {
@@ -651,6 +654,22 @@ __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__
 			for (int e = 0; e < E; ++e) mx = fmaxf(mx, sc[e]);
 			for (int e = 0; e < E; ++e) sum += expf(sc[e] - mx);
 		}
+		if (groups > 1 && keep < groups) {
+			// a group's rank is its best logit; groups outside the `keep` best lose all their experts
+			float *gbest = sc + E; // groups
+			const int per = E / groups;
+			for (int g = 0; g < groups; ++g) {
+				float b = -INFINITY;
+				for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, sc[e]);
+				gbest[g] = b;
+			}
+			for (int g = 0; g < groups; ++g) {
+				int better = 0;
+				for (int o = 0; o < groups; ++o) better += (gbest[o] > gbest[g]) || (gbest[o] == gbest[g] && o < g);
+				if (better >= keep)
+					for (int e = g * per; e < (g + 1) * per; ++e) sc[e] = -INFINITY;
+			}
+		}
 		float tot = 0.f;
 		for (int j = 0; j < top; ++j) {
 			int best = -1;
@@ -664,7 +683,7 @@ __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__
 			sc[best] = -INFINITY;
 		}
 		if (renorm)
-			for (int j = 0; j < top; ++j) wts[(size_t)m * top + j] /= tot;
+			for (int j = 0; j < top; ++j) wts[(size_t)m * top + j] /= tot + renorm_eps;
 	}
 }
 
@@ -738,9 +757,9 @@ static inline int elem_size(int dtype) { return dtype == YALM_F32 ? 4 : 2; }
 static inline bool row_vec(const void *w, int K, int dtype) { return aligned16(w) && ((size_t)K * elem_size(dtype)) % 16 == 0; }
 
 extern "C" int yalm_embed_rows(float *x, const void *table, const void *positions, int dtype, const int *tokens, int n, int dim, int pos0,
-                               const int *ctl, yalm_stream_t s) {
+                               const int *ctl, float scale, yalm_stream_t s) {
 	if (!x || !table || n < 1 || dim < 1 || (!tokens && !ctl)) return YALM_EINVAL;
-	DISPATCH_DT(dtype, (embed_rows_kernel<DT><<<n, 256, 0, (cudaStream_t)s>>>(x, table, positions, tokens, dim, pos0, ctl)));
+	DISPATCH_DT(dtype, (embed_rows_kernel<DT><<<n, 256, 0, (cudaStream_t)s>>>(x, table, positions, tokens, dim, pos0, ctl, scale)));
 	return (int)cudaGetLastError();
 }
 
@@ -890,10 +909,10 @@ extern "C" int yalm_norm_residual_rows(float *x, const float *y, int ldy, int ns
 	return (int)cudaGetLastError();
 }
 
-extern "C" int yalm_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, float w_offset, float eps, int n_rows, int dim,
-                                     yalm_stream_t s) {
+extern "C" int yalm_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, int scalar_weight, float w_offset, float eps, int n_rows,
+                                     int dim, yalm_stream_t s) {
 	if (!out || !x || !w || n_rows < 1) return YALM_EINVAL;
-	norm_gather_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)s>>>(out, x, rows, w, w_offset, eps, dim);
+	norm_gather_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)s>>>(out, x, rows, w, scalar_weight, w_offset, eps, dim);
 	return (int)cudaGetLastError();
 }
 
@@ -906,11 +925,13 @@ extern "C" int yalm_glu_act_rows(float *h, const float *gu, int n, int ff, int a
 
 // score: 0 softmax, 1 sigmoid
 extern "C" int yalm_router_topk_rows(int *ids, float *wts, const float *x, int ldx, const void *wr, int dtype, int n, int n_experts, int top, int dim,
-                                     int score, int renorm, yalm_stream_t s) {
-	if (!ids || !wts || !x || !wr || n < 1 || top < 1 || top > n_experts || n_experts > 1024) return YALM_EINVAL;
+                                     int score, int renorm, float renorm_eps, int groups, int keep_groups, yalm_stream_t s) {
+	if (!ids || !wts || !x || !wr || n < 1 || top < 1 || top > n_experts || n_experts > 1024 || groups < 1 || n_experts % groups || keep_groups < 1 ||
+	    keep_groups > groups || top > keep_groups * (n_experts / groups))
+		return YALM_EINVAL;
 	const bool vec = row_vec(wr, dim, dtype) && aligned16(x) && ldx % 4 == 0;
-	DISPATCH_DT(dtype, (router_topk_rows_kernel<DT><<<n, 128, sizeof(float) * n_experts, (cudaStream_t)s>>>(ids, wts, x, ldx, wr, n_experts, top, dim,
-	                                                                                                      score, renorm, vec)));
+	DISPATCH_DT(dtype, (router_topk_rows_kernel<DT><<<n, 128, sizeof(float) * (n_experts + groups), (cudaStream_t)s>>>(
+	                       ids, wts, x, ldx, wr, n_experts, top, dim, score, renorm, renorm_eps, groups, keep_groups, vec)));
 	return (int)cudaGetLastError();
 }
 

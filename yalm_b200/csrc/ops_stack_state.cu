@@ -1,0 +1,550 @@
+// Row-batched ops of the layered executor (stack.cpp) for layers that carry per-sequence state besides a key / value ring:
+// token shift, short causal convolutions, linear recurrences over a matrix state (state-space and gated-delta-rule mixers),
+// and the sigmoid-weighted windowed attention.  As in ops_stack.cu every op takes M rows = M consecutive positions of one
+// sequence (M = 1: a decode step; M > 1: a portion of a prompt cut anywhere) and runs the same arithmetic for both; what a
+// sequence carries from one call to the next lives in fp32 state buffers owned by the model.  A call whose first position
+// is 0 starts a sequence: the stored state is ignored (taken as zero), so giving a sequence's state back needs no clearing.
+//
+// Mechanisms (constants are parameters):
+//   norm_shift_rows        h = rms(x) * w (one weight per channel or one number) and, optionally, the token-shifted copy
+//                          hs = h + (h of the previous position - h) * mu
+//   conv_act_rows          per-channel causal convolution over the last `taps` positions (+ bias) and SiLU
+//   state_scan_rows        S <- decay * S;  u = beta (v - S^T k)  or  u = vscale * v;  S <- S + k u^T;  o = S^T q (+ skip * v)
+//                          with a scalar or per-key-channel decay: both the state-space recurrence and the gated delta rule
+//   ssm_prep_rows          dt = softplus(raw + bias), decay = exp(-exp(A_log) dt)
+//   delta_prep_rows        unit q / k per head, beta = sigmoid(raw), per-channel decay from raw step sizes
+//   gated_group_norm_rows  rms over equal parts of (y * silu(z)), times a weight
+//   head_norm_gate_rows    per head rms(o) * w * sigmoid(gate)
+//   qk_bias_append_rows    projection biases, key append to the ring and to the kept-first buffer
+//   attn_sigmoid_rows      window + kept first tokens, weights sigmoid(q.k scale + distance bias + head bias), values = keys,
+//                          sigmoid output gate
+//   residual_sum_rows      x += a (+ b) + sum of partial outputs
+//   softcap_rows           z <- cap * tanh(z / cap)
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "launch.h"
+#include "stack_rows.cuh"
+
+namespace yalm {
+namespace stack {
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
+
+// ---- norm + token shift --------------------------------------------------------------------------------------------------
+// One CTA per row.  The previous position's h of row m > 0 is recomputed from x[m - 1]; row 0 takes it from `state` (zero at
+// position 0).  update != 0 (single-row calls only: no other CTA reads the state): the row's h becomes the state; calls with
+// more rows copy their last h row afterwards.  h may alias x only when hs is null.
+__global__ void __launch_bounds__(256) norm_shift_rows_kernel(float *__restrict__ h, float *__restrict__ hs, const float *x, const float *__restrict__ w,
+                                                              int scalar, float woff, float eps, const float *__restrict__ mu, float *state, int update,
+                                                              int dim, int pos0, const int *__restrict__ ctl) {
+	__shared__ float red[33];
+	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m;
+	const float *xr = x + (size_t)m * dim, *xp = xr - dim;
+	float ss = 0.f, sp = 0.f;
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+		ss += xr[e] * xr[e];
+		if (hs && m > 0) sp += xp[e] * xp[e];
+	}
+	ss = block_sum(ss, red);
+	const float r = 1.0f / sqrtf(ss / dim + eps);
+	float rp = 0.f;
+	if (hs && m > 0) rp = 1.0f / sqrtf(block_sum(sp, red) / dim + eps);
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+		const float g = woff + (scalar ? w[0] : w[e]);
+		const float v = xr[e] * r * g;
+		if (hs) {
+			const float prev = m > 0 ? xp[e] * rp * g : (p > 0 ? state[e] : 0.f);
+			hs[(size_t)m * dim + e] = v + (prev - v) * mu[e];
+			if (update) state[e] = v;
+		}
+		h[(size_t)m * dim + e] = v;
+	}
+}
+
+// ---- short causal convolution + SiLU ---------------------------------------------------------------------------------------
+// out[m, c] = silu(b[c] + sum_j w[c, j] in[m - (taps - 1) + j, c]); rows before the call's first come from the state
+// (C, taps - 1), which holds the inputs of positions p0 - (taps - 1) .. p0 - 1; positions before 0 are zero.
+__device__ __forceinline__ float conv_input(const float *in, int ldi, const float *state, int c, int taps, int row, int p0) {
+	if (row >= 0) return in[(size_t)row * ldi + c];
+	return p0 + row >= 0 ? state[(size_t)c * (taps - 1) + (taps - 1) + row] : 0.f;
+}
+// new state slot s = the input of row n - (taps - 1) + s; ascending s only reads old slots above s
+__device__ __forceinline__ void conv_state_update(const float *in, int ldi, float *state, int c, int taps, int n, int p0) {
+	for (int s = 0; s < taps - 1; ++s) state[(size_t)c * (taps - 1) + s] = conv_input(in, ldi, state, c, taps, n - (taps - 1) + s, p0);
+}
+constexpr int kConvRows = 32;
+__global__ void __launch_bounds__(128) conv_act_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ in, int ldi,
+                                                            const float *__restrict__ w, const float *__restrict__ bias, float *state, int n, int C,
+                                                            int taps, int pos0, const int *__restrict__ ctl) {
+	const int c = blockIdx.x * blockDim.x + threadIdx.x;
+	if (c >= C) return;
+	const int p0 = first_pos(ctl, pos0);
+	const int m0 = blockIdx.y * kConvRows, m1 = min(n, m0 + kConvRows);
+	const float b = bias ? bias[c] : 0.f;
+	for (int m = m0; m < m1; ++m) {
+		float acc = b;
+		for (int j = 0; j < taps; ++j) acc = fmaf(w[(size_t)c * taps + j], conv_input(in, ldi, state, c, taps, m - (taps - 1) + j, p0), acc);
+		out[(size_t)m * ldo + c] = siluf_(acc);
+	}
+	if (gridDim.y == 1) conv_state_update(in, ldi, state, c, taps, n, p0); // this thread is the only reader of its channel's state
+}
+__global__ void __launch_bounds__(128) conv_state_rows_kernel(const float *__restrict__ in, int ldi, float *state, int n, int C, int taps, int pos0,
+                                                              const int *__restrict__ ctl) {
+	const int c = blockIdx.x * blockDim.x + threadIdx.x;
+	if (c < C) conv_state_update(in, ldi, state, c, taps, n, first_pos(ctl, pos0));
+}
+
+// ---- linear recurrence over a matrix state -----------------------------------------------------------------------------------
+// Per head a (D, P) matrix S whose columns evolve independently:
+//   S <- decay * S   (decay: one number per head, or one per head and key channel, acting on rows)
+//   u = beta * (v - S^T k)   (delta rule)   or   u = vscale * v
+//   S <- S + k u^T;   o = S^T q  (+ skip * v)
+// One CTA owns 16 columns of one head; 8 neighbouring lanes share a column, lane `sub` holding the rows e * 8 + sub in
+// registers, so the two dot products of a step are EPL multiply-adds and three shuffles.  k, q, the decays and v of 8
+// positions are staged in shared memory at a time.  The order of every sum is fixed, so a position's output does not depend
+// on how the rows were cut into calls.  State in global memory: (head, column, row) fp32.
+struct ScanArgs {
+	float *out;
+	int ldo;
+	const float *k, *q, *v, *decay, *vscale, *beta, *skip;
+	int ldk, ldq, ldv, ldd, ldvs, ldb;
+	int decay_per_channel;
+	float *state;
+	int n, H, rep, D, P, pos0;
+	const int *ctl;
+};
+constexpr int kScanCols = 16, kScanTok = 8, kScanMaxD = 256;
+
+template <int EPL>
+__global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
+	constexpr int DP = EPL * 8;
+	__shared__ __align__(16) float ks[kScanTok * kScanMaxD], qs[kScanTok * kScanMaxD], gs[kScanTok * kScanMaxD];
+	__shared__ float vs[kScanTok][kScanCols], sc[kScanTok][3];
+	const int h = blockIdx.y, kh = h / a.rep, c0 = blockIdx.x * kScanCols;
+	const int tid = threadIdx.x, col = tid >> 3, sub = tid & 7;
+	const bool live = c0 + col < a.P;
+	const bool fresh = first_pos(a.ctl, a.pos0) == 0;
+	float *sp = a.state + ((size_t)h * a.P + min(c0 + col, a.P - 1)) * a.D;
+	float s[EPL];
+#pragma unroll
+	for (int e = 0; e < EPL; ++e) s[e] = (!fresh && e * 8 + sub < a.D) ? sp[e * 8 + sub] : 0.f;
+	const float skip = a.skip ? a.skip[h] : 0.f;
+	for (int t0 = 0; t0 < a.n; t0 += kScanTok) {
+		const int tc = min(kScanTok, a.n - t0);
+		__syncthreads(); // the previous positions have been consumed
+		for (int idx = tid; idx < tc * DP; idx += blockDim.x) {
+			const int t = idx / DP, i = idx % DP;
+			const bool in = i < a.D;
+			ks[idx] = in ? a.k[(size_t)(t0 + t) * a.ldk + kh * a.D + i] : 0.f;
+			qs[idx] = in ? a.q[(size_t)(t0 + t) * a.ldq + kh * a.D + i] : 0.f;
+			if (a.decay_per_channel) gs[idx] = in ? a.decay[(size_t)(t0 + t) * a.ldd + h * a.D + i] : 0.f;
+		}
+		for (int idx = tid; idx < tc * kScanCols; idx += blockDim.x) {
+			const int t = idx / kScanCols, c = idx % kScanCols;
+			vs[t][c] = c0 + c < a.P ? a.v[(size_t)(t0 + t) * a.ldv + h * a.P + c0 + c] : 0.f;
+		}
+		if (tid < tc) {
+			sc[tid][0] = a.decay_per_channel ? 1.f : a.decay[(size_t)(t0 + tid) * a.ldd + h];
+			sc[tid][1] = a.vscale ? a.vscale[(size_t)(t0 + tid) * a.ldvs + h] : 1.f;
+			sc[tid][2] = a.beta ? a.beta[(size_t)(t0 + tid) * a.ldb + h] : 0.f;
+		}
+		__syncthreads();
+		for (int t = 0; t < tc; ++t) {
+			const float *kt = ks + t * DP + sub, *qt = qs + t * DP + sub, *gt = gs + t * DP + sub;
+			const float vv = vs[t][col];
+			if (a.decay_per_channel) {
+#pragma unroll
+				for (int e = 0; e < EPL; ++e) s[e] *= gt[e * 8];
+			} else {
+				const float d = sc[t][0];
+#pragma unroll
+				for (int e = 0; e < EPL; ++e) s[e] *= d;
+			}
+			float u;
+			if (a.beta) {
+				float dot = 0.f;
+#pragma unroll
+				for (int e = 0; e < EPL; ++e) dot = fmaf(s[e], kt[e * 8], dot);
+				dot += __shfl_xor_sync(kFull, dot, 4), dot += __shfl_xor_sync(kFull, dot, 2), dot += __shfl_xor_sync(kFull, dot, 1);
+				u = sc[t][2] * (vv - dot);
+			} else
+				u = sc[t][1] * vv;
+			float o = 0.f;
+#pragma unroll
+			for (int e = 0; e < EPL; ++e) {
+				s[e] = fmaf(kt[e * 8], u, s[e]);
+				o = fmaf(s[e], qt[e * 8], o);
+			}
+			o += __shfl_xor_sync(kFull, o, 4), o += __shfl_xor_sync(kFull, o, 2), o += __shfl_xor_sync(kFull, o, 1);
+			if (sub == 0 && live) a.out[(size_t)(t0 + t) * a.ldo + h * a.P + c0 + col] = o + skip * vv;
+		}
+	}
+	if (live) {
+#pragma unroll
+		for (int e = 0; e < EPL; ++e)
+			if (e * 8 + sub < a.D) sp[e * 8 + sub] = s[e];
+	}
+}
+
+// dt[m, h] = softplus(dt + bias[h]) in place; decay[m, h] = exp(-exp(a_log[h]) * dt)
+__global__ void ssm_prep_rows_kernel(float *__restrict__ dt, int lddt, float *__restrict__ decay, int ldd, const float *__restrict__ bias,
+                                     const float *__restrict__ a_log, int H) {
+	const int m = blockIdx.x;
+	for (int h = threadIdx.x; h < H; h += blockDim.x) {
+		const float d = softplusf_(dt[(size_t)m * lddt + h] + bias[h]);
+		dt[(size_t)m * lddt + h] = d;
+		decay[(size_t)m * ldd + h] = expf(-expf(a_log[h]) * d);
+	}
+}
+
+// One CTA per row.  q, k (G heads of D, row stride ldqk, in place): x / sqrt(sum x^2 + unit_eps), q also times q_scale.
+// beta (H, in place) = sigmoid(raw).  g (H * D, in place) = exp(-exp(a_log[h]) * softplus(raw + dt_bias)).
+__global__ void __launch_bounds__(256) delta_prep_rows_kernel(float *__restrict__ q, float *__restrict__ k, int ldqk, float *__restrict__ beta, int ldb,
+                                                              float *__restrict__ g, int ldg, const float *__restrict__ a_log,
+                                                              const float *__restrict__ dt_bias, int H, int G, int D, float unit_eps, float q_scale) {
+	const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+	for (int j = warp; j < 2 * G; j += nw) {
+		float *row = (j < G ? q + (size_t)m * ldqk + j * D : k + (size_t)m * ldqk + (j - G) * D);
+		float ss = 0.f;
+		for (int i = lane; i < D; i += 32) ss += row[i] * row[i];
+		ss = warp_sum(ss);
+		const float r = (j < G ? q_scale : 1.f) / sqrtf(ss + unit_eps);
+		for (int i = lane; i < D; i += 32) row[i] *= r;
+	}
+	for (int h = threadIdx.x; h < H; h += blockDim.x) beta[(size_t)m * ldb + h] = sigmoidf_(beta[(size_t)m * ldb + h]);
+	for (int e = threadIdx.x; e < H * D; e += blockDim.x) {
+		const float step = softplusf_(g[(size_t)m * ldg + e] + dt_bias[e]);
+		g[(size_t)m * ldg + e] = expf(-expf(a_log[e / D]) * step);
+	}
+}
+
+// out[m, c] = rms_part(y[m, c] * silu(z[m, c])) * w[c], the row cut into gridDim.y equal parts.  grid (rows, parts).
+__global__ void __launch_bounds__(256) gated_group_norm_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ y, int ldy,
+                                                                    const float *__restrict__ z, int ldz, const float *__restrict__ w, int part, float eps) {
+	__shared__ float red[33];
+	const int m = blockIdx.x, c0 = blockIdx.y * part;
+	float ss = 0.f;
+	for (int c = threadIdx.x; c < part; c += blockDim.x) {
+		const float v = y[(size_t)m * ldy + c0 + c] * siluf_(z[(size_t)m * ldz + c0 + c]);
+		ss += v * v;
+	}
+	ss = block_sum(ss, red);
+	const float r = 1.0f / sqrtf(ss / part + eps);
+	for (int c = threadIdx.x; c < part; c += blockDim.x)
+		out[(size_t)m * ldo + c0 + c] = y[(size_t)m * ldy + c0 + c] * siluf_(z[(size_t)m * ldz + c0 + c]) * r * w[c0 + c];
+}
+
+// out[m, h, c] = o / sqrt(mean_c o^2 + eps) * w[c] * sigmoid(gate[m, h, c]); one warp per (row, head), w shared by the heads
+__global__ void __launch_bounds__(128) head_norm_gate_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ o, int ldi,
+                                                                  const float *__restrict__ gate, int ldg, const float *__restrict__ w, int H, int P,
+                                                                  float eps) {
+	const int m = blockIdx.y, h = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+	if (h >= H) return;
+	const float *row = o + (size_t)m * ldi + h * P;
+	float ss = 0.f;
+	for (int c = lane; c < P; c += 32) ss += row[c] * row[c];
+	ss = warp_sum(ss);
+	const float r = 1.0f / sqrtf(ss / P + eps);
+	for (int c = lane; c < P; c += 32) out[(size_t)m * ldo + h * P + c] = row[c] * r * w[c] * sigmoidf_(gate[(size_t)m * ldg + h * P + c]);
+}
+
+// ---- sigmoid attention -----------------------------------------------------------------------------------------------------
+// q += qb, k += kb (in place, fp32); k goes to ring slot p % ring and, for the sequence's first `keep` positions, also to the
+// kept-first buffer (kv head, keep, channel), which the ring's reuse never touches.
+template <typename CT>
+__global__ void __launch_bounds__(256) qk_bias_append_rows_kernel(float *__restrict__ q, float *__restrict__ k, int ld, const float *__restrict__ qb,
+                                                                  const float *__restrict__ kb, CT *__restrict__ ring_buf, CT *__restrict__ first_buf,
+                                                                  int nq, int nk, int dk, int ring, int keep, int pos0, const int *__restrict__ ctl) {
+	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m, slot = p % ring;
+	if (qb)
+		for (int e = threadIdx.x; e < nq; e += blockDim.x) q[(size_t)m * ld + e] += qb[e];
+	for (int e = threadIdx.x; e < nk; e += blockDim.x) {
+		const float v = k[(size_t)m * ld + e] + (kb ? kb[e] : 0.f);
+		k[(size_t)m * ld + e] = v;
+		const int g = e / dk, d = e % dk;
+		cache_put(ring_buf, ((size_t)g * ring + slot) * dk + d, v);
+		if (p < keep) cache_put(first_buf, ((size_t)g * keep + p) * dk + d, v);
+	}
+}
+
+// Query row m at position i sees the positions lo .. i (lo = max(0, i - window + 1); window 0: lo = 0) from the ring and the
+// positions 0 .. min(keep, lo) - 1 from the kept-first buffer, each at its true distance i - j.  The weight of a key is
+// sigmoid(q . k * scale + rel[bucket[i - j], h] + hb[h]); weights are not normalised, the values are the keys, and the
+// result is multiplied by sigmoid(gate) (gate null: not).  One CTA per (kv head x up to R query heads that share it, row,
+// split); its warps take 32-key tiles in turn, lane = key for the scores and lane = channel for the weighted sum.  With
+// splits (few rows: decoding) a CTA leaves its partial sum in `part` and attn_sigmoid_merge_kernel adds the splits in order.
+constexpr int kSigWarps = 4;
+template <typename CT, int R, int DVC>
+__global__ void __launch_bounds__(kSigWarps * 32) attn_sigmoid_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                                           const CT *__restrict__ ring_buf, const CT *__restrict__ first_buf,
+                                                                           const float *__restrict__ gate, int ldg, const float *__restrict__ rel,
+                                                                           const int *__restrict__ bucket, const float *__restrict__ hb,
+                                                                           float *__restrict__ part, int n_heads, int n_kv, int dk, int ring, int window,
+                                                                           int keep, float scale, int pos0, const int *__restrict__ ctl) {
+	extern __shared__ __align__(16) float sm[];
+	const int dkp = (dk + 3) & ~3;
+	float *qs = sm;                 // R x dkp
+	float *macc = qs + R * dkp;     // kSigWarps x R x dk
+	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
+	const int g = blockIdx.x / hg, h0 = g * rep + (blockIdx.x % hg) * R, nh = min(R, g * rep + rep - h0);
+	const int m = blockIdx.y, z = blockIdx.z, nsplit = gridDim.z;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int i = first_pos(ctl, pos0) + m;
+	const int lo = window > 0 ? max(0, i - window + 1) : 0;
+	const int nfirst = min(keep, lo), ntok = i - lo + 1;
+	for (int e = threadIdx.x; e < R * dkp; e += blockDim.x) {
+		const int r = e / dkp, d = e % dkp;
+		qs[e] = (r < nh && d < dk) ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
+	}
+	__syncthreads();
+	const CT *rbase = ring_buf + (size_t)g * ring * dk, *fbase = first_buf ? first_buf + (size_t)g * keep * dk : nullptr;
+	float bias_h[R];
+#pragma unroll
+	for (int r = 0; r < R; ++r) bias_h[r] = (hb && r < nh) ? hb[h0 + r] : 0.f;
+	float acc[R][DVC];
+#pragma unroll
+	for (int r = 0; r < R; ++r)
+#pragma unroll
+		for (int c = 0; c < DVC; ++c) acc[r][c] = 0.f;
+	// kept-first keys and window keys occupy separate 32-key tiles
+	const int ftiles = (nfirst + 31) / 32, ntiles = ftiles + (ntok + 31) / 32, per = (ntiles + nsplit - 1) / nsplit;
+	const int t_end = min(ntiles, (z + 1) * per);
+	for (int t = z * per + warp; t < t_end; t += kSigWarps) {
+		const bool first = t < ftiles;
+		const int idx0 = first ? t * 32 : (t - ftiles) * 32, cnt = min(32, (first ? nfirst : ntok) - idx0);
+		const int j = first ? idx0 + lane : lo + idx0 + lane; // this lane's key position
+		float p[R];
+#pragma unroll
+		for (int r = 0; r < R; ++r) p[r] = 0.f;
+		if (lane < cnt) {
+			const CT *krow = first ? fbase + (size_t)j * dk : rbase + (size_t)(j % ring) * dk;
+			float s[R];
+#pragma unroll
+			for (int r = 0; r < R; ++r) s[r] = 0.f;
+			for (int d = 0; d < dk; ++d) {
+				const float kv = cache_get(krow, d);
+#pragma unroll
+				for (int r = 0; r < R; ++r) s[r] = fmaf(kv, qs[r * dkp + d], s[r]);
+			}
+			const int b = bucket ? bucket[i - j] : 0;
+#pragma unroll
+			for (int r = 0; r < R; ++r)
+				if (r < nh) p[r] = sigmoidf_(s[r] + (rel ? rel[(size_t)b * n_heads + h0 + r] : 0.f) + bias_h[r]);
+		}
+		constexpr int KU = 8;
+		for (int k0 = 0; k0 < cnt; k0 += KU) {
+			float vv[KU][DVC];
+#pragma unroll
+			for (int u = 0; u < KU; ++u) {
+				const int kk = min(k0 + u, cnt - 1); // past the end: a repeated row whose weight is zero
+				const int jj = first ? idx0 + kk : lo + idx0 + kk;
+				const CT *vr = first ? fbase + (size_t)jj * dk : rbase + (size_t)(jj % ring) * dk;
+#pragma unroll
+				for (int c = 0; c < DVC; ++c) vv[u][c] = c * 32 + lane < dk ? cache_get(vr, c * 32 + lane) : 0.f;
+			}
+#pragma unroll
+			for (int u = 0; u < KU; ++u)
+#pragma unroll
+				for (int r = 0; r < R; ++r) {
+					const float pk = k0 + u < cnt ? __shfl_sync(kFull, p[r], (k0 + u) & 31) : 0.f;
+#pragma unroll
+					for (int c = 0; c < DVC; ++c) acc[r][c] = fmaf(pk, vv[u][c], acc[r][c]);
+				}
+		}
+	}
+#pragma unroll
+	for (int r = 0; r < R; ++r)
+#pragma unroll
+		for (int c = 0; c < DVC; ++c)
+			if (c * 32 + lane < dk) macc[(warp * R + r) * dk + c * 32 + lane] = acc[r][c];
+	__syncthreads();
+	for (int e = threadIdx.x; e < nh * dk; e += blockDim.x) {
+		const int r = e / dk, c = e % dk, h = h0 + r;
+		float o = 0.f;
+		for (int w = 0; w < kSigWarps; ++w) o += macc[(w * R + r) * dk + c];
+		if (part) part[((size_t)(m * n_heads + h) * nsplit + z) * dk + c] = o;
+		else out[(size_t)m * ldo + (size_t)h * dk + c] = gate ? o * sigmoidf_(gate[(size_t)m * ldg + (size_t)h * dk + c]) : o;
+	}
+}
+__global__ void attn_sigmoid_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, const float *__restrict__ gate, int ldg,
+                                          int n_heads, int dk, int nsplit) {
+	const int h = blockIdx.x, m = blockIdx.y;
+	const float *pr = part + (size_t)(m * n_heads + h) * nsplit * dk;
+	for (int c = threadIdx.x; c < dk; c += blockDim.x) {
+		float o = 0.f;
+		for (int z = 0; z < nsplit; ++z) o += pr[(size_t)z * dk + c];
+		out[(size_t)m * ldo + (size_t)h * dk + c] = gate ? o * sigmoidf_(gate[(size_t)m * ldg + (size_t)h * dk + c]) : o;
+	}
+}
+
+// ---- x += a (+ b) + sum_j y_j -------------------------------------------------------------------------------------------------
+__global__ void residual_sum_rows_kernel(float *__restrict__ x, const float *__restrict__ a, const float *__restrict__ b, const float *__restrict__ y,
+                                         int ldy, int nsum, int dim) {
+	const int m = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+	if (e >= dim) return;
+	float v = a ? a[(size_t)m * dim + e] : 0.f;
+	if (b) v += b[(size_t)m * dim + e];
+	float f = 0.f;
+	for (int j = 0; j < nsum; ++j) f += y[((size_t)m * nsum + j) * ldy + e];
+	x[(size_t)m * dim + e] += v + f;
+}
+
+__global__ void softcap_rows_kernel(float *__restrict__ z, size_t count, float cap) {
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i < count) z[i] = cap * tanhf(z[i] / cap);
+}
+
+} // namespace stack
+} // namespace yalm
+
+using namespace yalm;
+using namespace yalm::stack;
+
+extern "C" int yalm_norm_shift_rows(float *h, float *hs, const float *x, const float *w, int scalar_weight, float w_offset, float eps, const float *shift,
+                                    float *state, int n, int dim, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!h || !x || !w || n < 1 || dim < 1 || (hs && (!shift || !state || h == x))) return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	norm_shift_rows_kernel<<<n, 256, 0, st>>>(h, hs, x, w, scalar_weight, w_offset, eps, shift, state, n == 1, dim, pos0, ctl);
+	if (hs && n > 1) return (int)cudaMemcpyAsync(state, h + (size_t)(n - 1) * dim, sizeof(float) * dim, cudaMemcpyDeviceToDevice, st);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_conv_act_rows(float *out, int ldo, const float *in, int ldi, const float *w, const float *bias, float *state, int n, int channels,
+                                  int taps, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!out || !in || !w || !state || n < 1 || channels < 1 || taps < 1 || out == in) return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	const dim3 grid((channels + 127) / 128, (n + kConvRows - 1) / kConvRows);
+	conv_act_rows_kernel<<<grid, 128, 0, st>>>(out, ldo, in, ldi, w, bias, state, n, channels, taps, pos0, ctl);
+	if (grid.y > 1 && taps > 1) conv_state_rows_kernel<<<grid.x, 128, 0, st>>>(in, ldi, state, n, channels, taps, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
+// See ScanArgs.  k, q: (n, kv heads * D) with head h reading kv head h / rep; v, out: (n, H * P); decay: (n, H) or, with
+// decay_per_channel, (n, H * D); vscale, beta: (n, H) or null; skip: (H) or null; state: (H, P, D) fp32.  D <= 256.
+extern "C" int yalm_state_scan_rows(float *out, int ldo, const float *k, int ldk, const float *q, int ldq, const float *v, int ldv, const float *decay,
+                                    int ldd, int decay_per_channel, const float *vscale, int ldvs, const float *beta, int ldb, const float *skip,
+                                    float *state, int n, int heads, int rep, int D, int P, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!out || !k || !q || !v || !decay || !state || n < 1 || heads < 1 || rep < 1 || heads % rep || D < 1 || D > kScanMaxD || P < 1) return YALM_EINVAL;
+	ScanArgs a{out, ldo, k, q, v, decay, vscale, beta, skip, ldk, ldq, ldv, ldd, ldvs, ldb, decay_per_channel, state, n, heads, rep, D, P, pos0, ctl};
+	const dim3 grid((P + kScanCols - 1) / kScanCols, heads);
+	cudaStream_t st = (cudaStream_t)s;
+	if (D <= 8) state_scan_kernel<1><<<grid, kScanCols * 8, 0, st>>>(a);
+	else if (D <= 16) state_scan_kernel<2><<<grid, kScanCols * 8, 0, st>>>(a);
+	else if (D <= 32) state_scan_kernel<4><<<grid, kScanCols * 8, 0, st>>>(a);
+	else if (D <= 64) state_scan_kernel<8><<<grid, kScanCols * 8, 0, st>>>(a);
+	else if (D <= 128) state_scan_kernel<16><<<grid, kScanCols * 8, 0, st>>>(a);
+	else state_scan_kernel<32><<<grid, kScanCols * 8, 0, st>>>(a);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_ssm_prep_rows(float *dt, int lddt, float *decay, int ldd, const float *dt_bias, const float *a_log, int n, int heads, yalm_stream_t s) {
+	if (!dt || !decay || !dt_bias || !a_log || n < 1 || heads < 1) return YALM_EINVAL;
+	ssm_prep_rows_kernel<<<n, 128, 0, (cudaStream_t)s>>>(dt, lddt, decay, ldd, dt_bias, a_log, heads);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_delta_prep_rows(float *q, float *k, int ldqk, float *beta, int ldb, float *g, int ldg, const float *a_log, const float *dt_bias, int n,
+                                    int heads, int kv_heads, int dim, float unit_eps, float q_scale, yalm_stream_t s) {
+	if (!q || !k || !beta || !g || !a_log || !dt_bias || n < 1 || heads < 1 || kv_heads < 1 || dim < 1) return YALM_EINVAL;
+	delta_prep_rows_kernel<<<n, 256, 0, (cudaStream_t)s>>>(q, k, ldqk, beta, ldb, g, ldg, a_log, dt_bias, heads, kv_heads, dim, unit_eps, q_scale);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_gated_group_norm_rows(float *out, int ldo, const float *y, int ldy, const float *z, int ldz, const float *w, int n, int dim, int parts,
+                                          float eps, yalm_stream_t s) {
+	if (!out || !y || !z || !w || n < 1 || parts < 1 || dim < parts || dim % parts) return YALM_EINVAL;
+	gated_group_norm_rows_kernel<<<dim3(n, parts), 256, 0, (cudaStream_t)s>>>(out, ldo, y, ldy, z, ldz, w, dim / parts, eps);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_head_norm_gate_rows(float *out, int ldo, const float *o, int ldi, const float *gate, int ldg, const float *w, int n, int heads, int vdim,
+                                        float eps, yalm_stream_t s) {
+	if (!out || !o || !gate || !w || n < 1 || heads < 1 || vdim < 1) return YALM_EINVAL;
+	head_norm_gate_rows_kernel<<<dim3((heads + 3) / 4, n), 128, 0, (cudaStream_t)s>>>(out, ldo, o, ldi, gate, ldg, w, heads, vdim, eps);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_qk_bias_append_rows(float *q, float *k, int ld, const float *qb, const float *kb, void *ring_buf, void *first_buf, int n, int n_heads,
+                                        int n_kv, int dk, int ring, int keep, int cache_f32, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!q || !k || !ring_buf || n < 1 || ring < 1 || keep < 0 || (keep > 0 && !first_buf)) return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	if (cache_f32)
+		qk_bias_append_rows_kernel<float><<<n, 256, 0, st>>>(q, k, ld, qb, kb, (float *)ring_buf, (float *)first_buf, n_heads * dk, n_kv * dk, dk, ring, keep,
+		                                                     pos0, ctl);
+	else
+		qk_bias_append_rows_kernel<__nv_bfloat16><<<n, 256, 0, st>>>(q, k, ld, qb, kb, (__nv_bfloat16 *)ring_buf, (__nv_bfloat16 *)first_buf, n_heads * dk,
+		                                                             n_kv * dk, dk, ring, keep, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
+constexpr int kSigMaxParts = 4096; // (row, head, split) partial sums the workspace holds
+extern "C" size_t yalm_attn_sigmoid_workspace(int dk) {
+	return (size_t)kSigMaxParts * dk;
+}
+
+template <typename CT, int R, int DVC>
+static int launch_attn_sigmoid(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
+                               const float *rel, const int *bucket, const float *hb, float *ws, int n, int n_heads, int n_kv, int dk, int ring, int window,
+                               int keep, float scale, int nsplit, int pos0, const int *ctl, cudaStream_t st) {
+	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
+	const size_t smem = sizeof(float) * ((size_t)R * ((dk + 3) & ~3) + (size_t)kSigWarps * R * dk);
+	if (smem > 48 * 1024) return YALM_EINVAL;
+	attn_sigmoid_rows_kernel<CT, R, DVC><<<dim3(n_kv * hg, n, nsplit), kSigWarps * 32, smem, st>>>(
+	    out, ldo, q, ldq, (const CT *)ring_buf, (const CT *)first_buf, gate, ldg, rel, bucket, hb, nsplit > 1 ? ws : nullptr, n_heads, n_kv, dk, ring, window,
+	    keep, scale, pos0, ctl);
+	if (nsplit > 1) attn_sigmoid_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, gate, ldg, n_heads, dk, nsplit);
+	return (int)cudaGetLastError();
+}
+
+// rel: (rows, n_heads) fp32 with bucket[distance] naming the row, or null; hb: (n_heads) or null; gate: (n, n_heads * dk)
+// raw gate values with row stride ldg, or null.  workspace: yalm_attn_sigmoid_workspace(dk) floats or null (never split);
+// context: the most positions a sequence reaches.
+extern "C" int yalm_attn_sigmoid_rows(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
+                                      const float *rel, const int *bucket, const float *hb, float *workspace, int n, int n_heads, int n_kv, int dk, int ring,
+                                      int window, int keep, float scale, int cache_f32, int context, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!out || !q || !ring_buf || n < 1 || n_kv < 1 || n_heads % n_kv || dk < 1 || dk > 256 || (keep > 0 && !first_buf) || (rel && !bucket)) return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	const int rep = n_heads / n_kv, R = rep >= 2 ? 4 : 1, hg = (rep + R - 1) / R;
+	int nsplit = 1;
+	const int ctas = n_kv * hg * n;
+	if (workspace && ctas < 296) { // few CTAs (decoding): split the keys; the count depends on shapes only, never on the position
+		const int most_keys = window > 0 ? window + keep : (context > 0 ? context : ring);
+		const int tiles = (most_keys + 31) / 32 + 1;
+		nsplit = std::min({(296 + ctas - 1) / ctas, std::max(1, (tiles + kSigWarps - 1) / kSigWarps), std::max(1, kSigMaxParts / (n * n_heads)), 64});
+	}
+#define SIG_CASE(CT, R_, DVC_)                                                                                                                     \
+	return launch_attn_sigmoid<CT, R_, DVC_>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, workspace, n, n_heads, n_kv, dk, ring, \
+	                                         window, keep, scale, nsplit, pos0, ctl, st)
+#define SIG_DVC(CT, R_)                                                                                                                            \
+	if (dk <= 64) SIG_CASE(CT, R_, 2);                                                                                                             \
+	else if (dk <= 128) SIG_CASE(CT, R_, 4);                                                                                                       \
+	else SIG_CASE(CT, R_, 8)
+	if (cache_f32) {
+		if (R == 1) { SIG_DVC(float, 1); }
+		else { SIG_DVC(float, 4); }
+	} else {
+		if (R == 1) { SIG_DVC(__nv_bfloat16, 1); }
+		else { SIG_DVC(__nv_bfloat16, 4); }
+	}
+#undef SIG_DVC
+#undef SIG_CASE
+}
+
+extern "C" int yalm_residual_sum_rows(float *x, const float *a, const float *b, const float *y, int ldy, int nsum, int n, int dim, yalm_stream_t s) {
+	if (!x || n < 1 || dim < 1 || nsum < 0 || (nsum && !y)) return YALM_EINVAL;
+	residual_sum_rows_kernel<<<dim3((dim + 255) / 256, n), 256, 0, (cudaStream_t)s>>>(x, a, b, y, ldy, nsum, dim);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_softcap_rows(float *z, int n, int dim, float cap, yalm_stream_t s) {
+	if (!z || n < 1 || dim < 1 || !(cap > 0.f)) return YALM_EINVAL;
+	const size_t count = (size_t)n * dim;
+	softcap_rows_kernel<<<(unsigned)((count + 255) / 256), 256, 0, (cudaStream_t)s>>>(z, count, cap);
+	return (int)cudaGetLastError();
+}

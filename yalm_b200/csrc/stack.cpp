@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -42,6 +43,28 @@ struct StackLayer {
 	float *kpool = nullptr, *vpool = nullptr; // (kv heads, max_blocks, dim | vdim)
 	int ring = 0, max_blocks = 0;
 	int vmode = 0;                           // 0 plain values, 1 the first blending layer, 2 a later one
+	// ---- parallel blocks: one packed projection of the mixer's input, then per-mixer pieces ----
+	void *wproj = nullptr;                   // (proj_width, dim); columns in the order of the o_* offsets below
+	float *shift = nullptr;                  // token-shift weight (dim)
+	float *conv_w = nullptr, *conv_b = nullptr; // short convolution (channels, taps) [+ bias]
+	// state-space mixer: columns [z | x | B | C | dt]
+	float *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr, *mix_norm = nullptr;
+	void *wout = nullptr;                    // state-space / delta-rule output projection
+	// sigmoid attention: columns [q | k | gate]
+	int o_q = 0, o_k = 0, o_gate = 0;
+	float *qkb = nullptr;                    // q bias then k bias
+	float *rel = nullptr, *head_bias = nullptr;
+	int *bucket = nullptr;                   // distance -> row of rel, max_seq_len entries
+	void *kfirst = nullptr;                  // (kv heads, keep_first, dim): the kept first tokens' keys
+	// delta rule: columns [q | k | v | beta | decay stage 1 | gate stage 1]
+	int o_dq = 0, o_beta = 0, o_a1 = 0, o_g1 = 0;
+	void *wa2 = nullptr, *wg2 = nullptr;     // second stages (heads * dim, rank), (heads * vdim, rank)
+	float *d_a_log = nullptr, *d_dt_bias = nullptr, *d_norm = nullptr;
+	// per-sequence state, fp32
+	float *hprev = nullptr;                  // the previous position's normed input (dim)
+	float *conv_state = nullptr;             // (channels, taps - 1)
+	float *scan_state = nullptr;             // (heads, vdim, state | dim)
+	std::vector<std::pair<void **, size_t>> state_allocs; // device buffers beside the rings, taken from the arena
 };
 
 } // namespace yalm
@@ -69,7 +92,25 @@ int Config::from_json(YALMData &data, int context, int compute) {
 	}
 	const int rc = a->configure(j, *this);
 	if (rc) return rc;
-	const StackSpec &s = *stack;
+	StackSpec &s = *stack;
+	for (int i = 0; i < (int)s.layers.size(); ++i) { // sizes that only the tensors give
+		yalm::LayerSpec &l = s.layers[i];
+		auto rows = [&](TensorRole role) {
+			const Tensor *t = data.find(s.tensor_name(i, role, -1));
+			return t ? t->shape[0] : 0;
+		};
+		if (l.kind == yalm::MixerKind::Parallel) {
+			l.delta.decay_rank = rows(TensorRole::DeltaDecay1), l.delta.gate_rank = rows(TensorRole::DeltaGate1);
+			if (l.delta.decay_rank < 1 || l.delta.gate_rank < 1) {
+				fprintf(stderr, "yalm_b200: layer %d: the delta rule's two-stage projections are missing\n", i);
+				return YALM_EFORMAT;
+			}
+		}
+		if (l.mix.rel_rows > 0 && (l.mix.rel_rows = rows(TensorRole::RelBias)) < 2) {
+			fprintf(stderr, "yalm_b200: layer %d: the distance-bias table needs at least two rows\n", i);
+			return YALM_EFORMAT;
+		}
+	}
 	const Tensor *emb = data.find(s.tensor_name(0, TensorRole::Embed, -1));
 	if (!emb) {
 		fprintf(stderr, "yalm_b200: the checkpoint has no embedding tensor\n");
@@ -170,6 +211,7 @@ struct Model::StackScratch {
 	float *x = nullptr, *qkv = nullptr, *vfirst = nullptr, *att = nullptr, *y = nullptr, *gu = nullptr, *h = nullptr, *wts = nullptr, *xn = nullptr,
 	      *logits = nullptr, *probs = nullptr;
 	void *a16 = nullptr;
+	float *hs = nullptr, *conv = nullptr, *aux = nullptr, *scan = nullptr, *att2 = nullptr, *y1 = nullptr, *y2 = nullptr; // parallel blocks
 	float *attn_ws = nullptr; // split partials of decode-sized attention calls
 	int *ids = nullptr, *tokens = nullptr, *want = nullptr, *targets = nullptr;
 	float *moe_gu = nullptr, *moe_ys = nullptr; // experts on the tensor cores: (gate | up) and down outputs of the slots sorted by expert
@@ -203,13 +245,101 @@ void Model::build_stack(YALMData &data) {
 
 	pl.push_back({&token_embedding_table, {mat(tensor(0, TensorRole::Embed, -1, {s.vocab, s.width}))}});
 	if (s.learned_positions) pl.push_back({&_pos_table, {mat(tensor(0, TensorRole::Positions, -1, {s.max_positions, s.width}))}});
-	pl.push_back({(void **)&rms_final_weight, {vec32(tensor(0, TensorRole::FinalNorm, -1, {s.width}))}});
+	pl.push_back({(void **)&rms_final_weight, {vec32(s.norm_scalar ? tensor(0, TensorRole::FinalNorm, -1, {}) : tensor(0, TensorRole::FinalNorm, -1, {s.width}))}});
+	if (s.embed_norm) pl.push_back({(void **)&_embed_norm, {vec32(s.norm_scalar ? tensor(0, TensorRole::EmbedNorm, -1, {}) : tensor(0, TensorRole::EmbedNorm, -1, {s.width}))}});
 	pl.push_back({&wcls, {mat(tensor(0, TensorRole::Head, -1, {s.vocab, s.width}))}});
 	bool have_first = false;
 	for (int i = 0; i < (int)s.layers.size(); ++i) {
 		auto L = std::make_shared<StackLayer>();
 		L->spec = s.layers[i];
 		const yalm::MixerSpec &m = L->spec.mix;
+		if (s.parallel_block) {
+			// ---- one norm, a packed projection of the mixer's input, per-mixer pieces, experts ----
+			const int W = s.width;
+			const yalm::LayerSpec &ls = L->spec;
+			pl.push_back({(void **)&L->norm1, {vec32(s.norm_scalar ? tensor(i, TensorRole::Norm1, -1, {}) : tensor(i, TensorRole::Norm1, -1, {W}))}});
+			if (s.token_shift) {
+				pl.push_back({(void **)&L->shift, {vec32(tensor(i, TensorRole::Shift, -1, {W}))}});
+				L->state_allocs.push_back({(void **)&L->hprev, (size_t)W * 4});
+			}
+			Placement proj{&L->wproj, {}};
+			if (ls.kind == yalm::MixerKind::StateSpace) {
+				const yalm::SsmSpec &q = ls.ssm;
+				const int C = q.conv_channels(), inner = q.inner();
+				proj.parts.push_back(mat(tensor(i, TensorRole::SsmIn, -1, {q.proj(), W})));
+				pl.push_back({(void **)&L->conv_w, {vec32(tensor(i, TensorRole::SsmConv, -1, {C, q.conv}))}});
+				pl.push_back({(void **)&L->conv_b, {vec32(tensor(i, TensorRole::SsmConvBias, -1, {C}))}});
+				pl.push_back({(void **)&L->dt_bias, {vec32(tensor(i, TensorRole::SsmDtBias, -1, {q.heads}))}});
+				pl.push_back({(void **)&L->a_log, {vec32(tensor(i, TensorRole::SsmALog, -1, {q.heads}))}});
+				pl.push_back({(void **)&L->skip, {vec32(tensor(i, TensorRole::SsmD, -1, {q.heads}))}});
+				pl.push_back({(void **)&L->mix_norm, {vec32(tensor(i, TensorRole::SsmNorm, -1, {inner}))}});
+				pl.push_back({&L->wout, {mat(tensor(i, TensorRole::SsmOut, -1, {W, inner}))}});
+				if (q.conv > 1) L->state_allocs.push_back({(void **)&L->conv_state, (size_t)C * (q.conv - 1) * 4});
+				L->state_allocs.push_back({(void **)&L->scan_state, (size_t)q.heads * q.vdim * q.state * 4});
+				if (q.state > 256) die("state-space mixer: state sizes above 256 are not built");
+			} else if (ls.kind == yalm::MixerKind::Parallel) {
+				const yalm::DeltaSpec &d = ls.delta;
+				const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, no = m.heads * m.vdim;
+				const int dk = d.kv_heads * d.dim, dv = d.heads * d.vdim, dg = d.heads * d.dim;
+				L->o_q = 0, L->o_k = nq, L->o_gate = nq + nk;
+				L->o_dq = L->o_gate + no, L->o_beta = L->o_dq + 2 * dk + dv, L->o_a1 = L->o_beta + d.heads, L->o_g1 = L->o_a1 + d.decay_rank;
+				proj.parts.push_back(mat(tensor(i, TensorRole::Wq, -1, {nq, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::Wk, -1, {nk, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::OutGate, -1, {no, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::DeltaQ, -1, {dk, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::DeltaK, -1, {dk, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::DeltaV, -1, {dv, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::DeltaBeta, -1, {d.heads, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::DeltaDecay1, -1, {d.decay_rank, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::DeltaGate1, -1, {d.gate_rank, W})));
+				pl.push_back({(void **)&L->qkb, {vec32(tensor(i, TensorRole::QBias, -1, {nq})), vec32(tensor(i, TensorRole::KBias, -1, {nk}))}});
+				pl.push_back({(void **)&L->rel, {vec32(tensor(i, TensorRole::RelBias, -1, {m.rel_rows, m.heads}))}});
+				pl.push_back({(void **)&L->head_bias, {vec32(tensor(i, TensorRole::HeadBias, -1, {m.heads}))}});
+				pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, no}))}});
+				{ // distance -> table row: exact below rows / 2, logarithmic up to rel_far, then the last row
+					const int rows = m.rel_rows, half = rows / 2;
+					if (m.rel_far <= half) die("distance bias: the farthest bucketed distance must exceed half the table");
+					_host_converted.emplace_back((size_t)c.max_seq_len * sizeof(int));
+					int *b = reinterpret_cast<int *>(_host_converted.back().data());
+					for (int n = 0; n < c.max_seq_len; ++n)
+						b[n] = n < half ? n
+						                : std::min(rows - 1, half + (int)std::floor(std::log((double)n / half) / std::log((double)m.rel_far / half) * (rows - half)));
+					pl.push_back({(void **)&L->bucket, {{b, (size_t)c.max_seq_len * sizeof(int)}}});
+				}
+				pl.push_back({(void **)&L->conv_w, {vec32(tensor(i, TensorRole::DeltaQConv, -1, {dk, d.conv})), vec32(tensor(i, TensorRole::DeltaKConv, -1, {dk, d.conv})),
+				                                    vec32(tensor(i, TensorRole::DeltaVConv, -1, {dv, d.conv}))}});
+				pl.push_back({(void **)&L->d_a_log, {vec32(tensor(i, TensorRole::DeltaALog, -1, {d.heads}))}});
+				pl.push_back({(void **)&L->d_dt_bias, {vec32(tensor(i, TensorRole::DeltaDtBias, -1, {dg}))}});
+				pl.push_back({(void **)&L->d_norm, {vec32(tensor(i, TensorRole::DeltaNorm, -1, {d.vdim}))}});
+				pl.push_back({&L->wa2, {mat(tensor(i, TensorRole::DeltaDecay2, -1, {dg, d.decay_rank}))}});
+				pl.push_back({&L->wg2, {mat(tensor(i, TensorRole::DeltaGate2, -1, {dv, d.gate_rank}))}});
+				pl.push_back({&L->wout, {mat(tensor(i, TensorRole::DeltaOut, -1, {W, dv}))}});
+				if (d.conv > 1) L->state_allocs.push_back({(void **)&L->conv_state, (size_t)(2 * dk + dv) * (d.conv - 1) * 4});
+				L->state_allocs.push_back({(void **)&L->scan_state, (size_t)d.heads * d.vdim * d.dim * 4});
+				if (d.dim > 256 || m.dim > 256) die("parallel mixer: head sizes above 256 are not built");
+				// the attention's keys (also its values): a ring for the window, a buffer for the kept first tokens
+				L->ring = m.window > 0 ? std::min(c.max_seq_len, (m.window + c.stack_chunk + 63) / 64 * 64) : c.max_seq_len;
+				const size_t cb = c.weight_dtype == DType::F32 ? 4 : 2;
+				L->state_allocs.push_back({&L->kring, (size_t)m.kv_heads * L->ring * m.dim * cb});
+				if (m.window > 0 && m.keep_first > 0) L->state_allocs.push_back({&L->kfirst, (size_t)m.kv_heads * m.keep_first * m.dim * cb});
+			} else
+				die("parallel blocks take a state-space or a parallel mixer");
+			pl.push_back(proj);
+			const FfnSpec &f = ls.ffn;
+			if (f.kind == FfnSpec::Moe) {
+				Placement g{&L->wg, {}}, u{&L->wu, {}}, dn{&L->wdown, {}};
+				for (int e = 0; e < f.experts; ++e) {
+					g.parts.push_back(mat(tensor(i, TensorRole::Gate, e, {f.ff, W})));
+					u.parts.push_back(mat(tensor(i, TensorRole::Up, e, {f.ff, W})));
+					dn.parts.push_back(mat(tensor(i, TensorRole::Down, e, {W, f.ff})));
+				}
+				pl.push_back(g), pl.push_back(u), pl.push_back(dn);
+				pl.push_back({&L->router, {mat(tensor(i, TensorRole::Router, -1, {f.experts, W}))}});
+			} else if (f.kind != FfnSpec::None)
+				die("parallel blocks take experts or no feed-forward");
+			_stack.push_back(L);
+			continue;
+		}
 		const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, no = m.heads * m.vdim, W = s.width;
 		pl.push_back({&L->wqkv,
 		              {mat(tensor(i, TensorRole::Wq, -1, {nq, W})), mat(tensor(i, TensorRole::Wk, -1, {nk, W})), mat(tensor(i, TensorRole::Wv, -1, {nv, W}))}});
@@ -267,6 +397,8 @@ void Model::cuda_stack(int device) {
 	for (const Placement &p : _scratch->placements) need += DeviceArena::padded(p.bytes());
 	for (auto &L : _stack) {
 		const yalm::MixerSpec &m = L->spec.mix;
+		for (auto &sa : L->state_allocs) need += DeviceArena::padded(sa.second);
+		if (s.parallel_block) continue;
 		need += DeviceArena::padded((size_t)m.kv_heads * L->ring * m.dim * cb) + DeviceArena::padded((size_t)m.kv_heads * L->ring * m.vdim * cb);
 		if (m.pool > 0)
 			need += DeviceArena::padded((size_t)m.kv_heads * L->max_blocks * m.dim * 4) + DeviceArena::padded((size_t)m.kv_heads * L->max_blocks * m.vdim * 4);
@@ -286,6 +418,12 @@ void Model::cuda_stack(int device) {
 	}
 	for (auto &L : _stack) {
 		const yalm::MixerSpec &m = L->spec.mix;
+		for (auto &sa : L->state_allocs) {
+			if (!(*sa.first = _arena->take(sa.second))) die("device arena exhausted (sequence state)");
+			up.zero(*sa.first, sa.second);
+			_device_bytes += sa.second;
+		}
+		if (s.parallel_block) continue;
 		const size_t kb = (size_t)m.kv_heads * L->ring * m.dim * cb, vb = (size_t)m.kv_heads * L->ring * m.vdim * cb;
 		L->kring = _arena->take(kb), L->vring = _arena->take(vb);
 		if (!L->kring || !L->vring) die("device arena exhausted (cache)");
@@ -308,7 +446,8 @@ void Model::cuda_stack(int device) {
 	StackScratch &S = *_scratch;
 	S.cap = c.stack_chunk;
 	const size_t cap = S.cap, W = s.width, top = std::max(1, s.max_top()), ff = std::max(1, s.max_ff());
-	const size_t nqkv = (size_t)s.max_q_dim() + s.max_kv_dim() + s.max_v_dim();
+	const size_t nqkv = std::max((size_t)s.max_q_dim() + s.max_kv_dim() + s.max_v_dim(), (size_t)s.max_proj());
+	const size_t pb = s.parallel_block ? 1 : 0, nconv = std::max(1, s.max_conv()), naux = std::max(1, s.max_aux()), no = std::max(1, s.max_o_dim());
 	const size_t kmax = std::max({W, (size_t)s.max_o_dim(), ff});
 	const bool moe = s.max_experts() > 0 && c.weight_dtype != DType::F32; // the grouped route needs 16-bit operands
 	auto pad = [](size_t b) { return (b + 255) / 256 * 256; };
@@ -322,6 +461,8 @@ void Model::cuda_stack(int device) {
 	             {(void **)&S.a16, 2 * cap * top * kmax}, {(void **)&S.ids, 4 * cap * top},       {(void **)&S.tokens, 4 * cap},
 	             {(void **)&S.want, 4 * cap},            {(void **)&S.targets, 4 * cap},
 	             {(void **)&S.attn_ws, 4 * yalm_attn_window_pool_workspace(256)}, {(void **)&S.ticket, 256},
+	             {(void **)&S.hs, pb * 4 * cap * W}, {(void **)&S.conv, pb * 4 * cap * nconv}, {(void **)&S.aux, pb * 4 * cap * naux},
+	             {(void **)&S.scan, pb * 4 * cap * no}, {(void **)&S.att2, pb * 4 * cap * no}, {(void **)&S.y1, pb * 4 * cap * W}, {(void **)&S.y2, pb * 4 * cap * W},
 	             {(void **)&S.moe_gu, moe ? 4 * cap * top * 2 * ff : 0}, {(void **)&S.moe_ys, moe ? 4 * cap * top * W : 0}, {(void **)&S.order, 4 * cap * top}};
 	size_t total = 0;
 	for (auto &sl : slots) total += pad(sl.bytes);
@@ -373,7 +514,7 @@ static bool moe_grouped_off() { // YALM_STACK_MOE_TC=0: A/B against the slot ker
 	return off;
 }
 
-int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, int n, int act, cudaStream_t st) {
+int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const float *x, int n, int act, cudaStream_t st) {
 	const Config &c = *config;
 	const FfnSpec &f = L.spec.ffn;
 	const int W = c.stack->width, ff = f.ff, top = f.top, E = f.experts, ns = n * top, bf16 = c.weight_dtype == DType::BF16;
@@ -390,7 +531,7 @@ int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, int n, 
 		for (int s = 0; s < ns; ++s) order[at[ids[s]]++] = s; // stable: slots of an expert stay in row order
 	}
 	ST_TRY(cudaMemcpyAsync(S.order, order.data(), sizeof(int) * ns, cudaMemcpyHostToDevice, st));
-	ST_TRY(yalm_moe_gather_rows16(S.a16, S.x, W, S.order, S.wts, ns, top, W, bf16, f.weight_on_input ? 1 : 0, st));
+	ST_TRY(yalm_moe_gather_rows16(S.a16, x, W, S.order, S.wts, ns, top, W, bf16, f.weight_on_input ? 1 : 0, st));
 	const size_t es = dtype_size(c.weight_dtype);
 	for (int e = 0; e < E; ++e) {
 		const int m = start[e + 1] - start[e];
@@ -412,6 +553,73 @@ int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, int n, 
 	return (int)cudaGetLastError(); // `order` was pageable host memory: the copy call returned after staging it
 }
 
+// One parallel block over n rows: h = norm(x); the mixer reads the token-shifted h through ONE packed projection, the experts
+// read h itself; x += mixer + experts.  What the rows leave for the next call (previous h, convolution tails, matrix states,
+// keys) is written by the ops themselves.
+int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int n, int pos0, const int *ctl, cudaStream_t st) {
+	const Config &c = *config;
+	const StackSpec &sp = *c.stack;
+	const yalm::LayerSpec &ls = L.spec;
+	const int dt = static_cast<int>(c.weight_dtype), W = sp.width, f32 = c.weight_dtype == DType::F32;
+	const float woff = sp.norm_one_plus ? 1.f : 0.f;
+	ST_TRY(yalm_norm_shift_rows(S.xn, sp.token_shift ? S.hs : nullptr, S.x, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, n, W, pos0, ctl, st));
+	const float *hin = sp.token_shift ? S.hs : S.xn;
+	const int ldp = ls.proj_width();
+	float *P = S.qkv;
+	ST_TRY(stack_linear(*this, c, S.a16, P, ldp, hin, W, L.wproj, n, ldp, W, 1.f, st));
+	const float *mix_b = nullptr;
+	if (ls.kind == yalm::MixerKind::StateSpace) {
+		const yalm::SsmSpec &q = ls.ssm;
+		const int inner = q.inner(), C = q.conv_channels(), gn = q.groups * q.state, o_dt = 2 * inner + 2 * gn;
+		ST_TRY(yalm_conv_act_rows(S.conv, C, P + inner, ldp, L.conv_w, L.conv_b, L.conv_state, n, C, q.conv, pos0, ctl, st));
+		ST_TRY(yalm_ssm_prep_rows(P + o_dt, ldp, S.aux, q.heads, L.dt_bias, L.a_log, n, q.heads, st));
+		ST_TRY(yalm_state_scan_rows(S.scan, inner, S.conv + inner, C, S.conv + inner + gn, C, S.conv, C, S.aux, q.heads, 0, P + o_dt, ldp, nullptr, 0, L.skip,
+		                            L.scan_state, n, q.heads, q.heads / q.groups, q.state, q.vdim, pos0, ctl, st));
+		ST_TRY(yalm_gated_group_norm_rows(S.att, inner, S.scan, inner, P, ldp, L.mix_norm, n, inner, q.norm_groups, sp.norm_eps, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, inner, L.wout, n, W, inner, 1.f, st));
+	} else {
+		// ---- left: sigmoid attention over the key ring and the kept first tokens ----
+		const yalm::MixerSpec &m = ls.mix;
+		const int nq = m.heads * m.dim, no = m.heads * m.vdim;
+		const int keep = m.window > 0 ? m.keep_first : 0;
+		ST_TRY(yalm_qk_bias_append_rows(P + L.o_q, P + L.o_k, ldp, L.qkb, L.qkb + nq, L.kring, L.kfirst, n, m.heads, m.kv_heads, m.dim, L.ring, keep, f32, pos0,
+		                                ctl, st));
+		ST_TRY(yalm_attn_sigmoid_rows(S.att, no, P + L.o_q, ldp, L.kring, L.kfirst, P + L.o_gate, ldp, L.rel, L.bucket, L.head_bias, S.attn_ws, n, m.heads,
+		                              m.kv_heads, m.dim, L.ring, m.window, keep, m.scale, f32, c.max_seq_len, pos0, ctl, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, no, L.wo, n, W, no, ls.left_scale, st));
+		// ---- right: gated delta rule ----
+		const yalm::DeltaSpec &d = ls.delta;
+		const int dk = d.kv_heads * d.dim, dv = d.heads * d.vdim, dg = d.heads * d.dim, C = 2 * dk + dv, lda = dg + dv;
+		ST_TRY(yalm_conv_act_rows(S.conv, C, P + L.o_dq, ldp, L.conv_w, nullptr, L.conv_state, n, C, d.conv, pos0, ctl, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.aux, lda, P + L.o_a1, ldp, L.wa2, n, dg, d.decay_rank, 1.f, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.aux + dg, lda, P + L.o_g1, ldp, L.wg2, n, dv, d.gate_rank, 1.f, st));
+		ST_TRY(yalm_delta_prep_rows(S.conv, S.conv + dk, C, P + L.o_beta, ldp, S.aux, lda, L.d_a_log, L.d_dt_bias, n, d.heads, d.kv_heads, d.dim, 1e-6f,
+		                            1.0f / sqrtf((float)d.dim), st));
+		ST_TRY(yalm_state_scan_rows(S.scan, dv, S.conv + dk, C, S.conv, C, S.conv + 2 * dk, C, S.aux, lda, 1, nullptr, 0, P + L.o_beta, ldp, nullptr,
+		                            L.scan_state, n, d.heads, d.heads / d.kv_heads, d.dim, d.vdim, pos0, ctl, st));
+		ST_TRY(yalm_head_norm_gate_rows(S.att2, dv, S.scan, dv, S.aux + dg, lda, L.d_norm, n, d.heads, d.vdim, sp.norm_eps, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.y2, W, S.att2, dv, L.wout, n, W, dv, ls.right_scale, st));
+		mix_b = S.y2;
+	}
+	// ---- experts on h ----
+	const FfnSpec &f = ls.ffn;
+	int nsum = 0;
+	if (f.kind == FfnSpec::Moe) {
+		const int act = f.act == yalm::GluAct::SigmoidScaled ? 2 : f.act == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
+		ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.xn, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
+		                             f.renormalize ? 1 : 0, f.renorm_eps, f.groups, f.keep_groups, st));
+		if (S.moe_gu && !ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
+			ST_TRY(stack_moe_grouped(S, L, S.xn, n, act, st));
+		else {
+			ST_TRY(yalm_moe_glu_slots(S.h, S.xn, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
+			                          f.weight_on_input ? 1 : 0, st));
+			ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
+		}
+		nsum = f.top;
+	}
+	return yalm_residual_sum_rows(S.x, S.y1, mix_b, S.y, W, nsum, n, W, st);
+}
+
 int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want) {
 	const Config &c = *config;
 	const StackSpec &sp = *c.stack;
@@ -420,9 +628,24 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 	const int dt = static_cast<int>(c.weight_dtype), W = sp.width, f32 = c.weight_dtype == DType::F32;
 	const int *ctl = from_ctl ? s.ctl() : nullptr;
 	const float woff = sp.norm_one_plus ? 1.f : 0.f;
-	ST_TRY(yalm_embed_rows(S.x, token_embedding_table, _pos_table, dt, from_ctl ? nullptr : S.tokens, n, W, pos0, ctl, st));
+	ST_TRY(yalm_embed_rows(S.x, token_embedding_table, _pos_table, dt, from_ctl ? nullptr : S.tokens, n, W, pos0, ctl, sp.embed_scale, st));
+	if (sp.embed_norm) ST_TRY(yalm_norm_shift_rows(S.x, nullptr, S.x, _embed_norm, sp.norm_scalar, woff, sp.norm_eps, nullptr, nullptr, n, W, pos0, ctl, st));
+	int layer_no = 0;
+	auto tap = [&]() -> int { // tests: the residual rows after this layer
+		if (_stack_tap && !from_ctl) {
+			ST_TRY(cudaMemcpyAsync(_stack_tap + (size_t)layer_no * n * W, S.x, sizeof(float) * n * W, cudaMemcpyDeviceToHost, st));
+			ST_TRY(cudaStreamSynchronize(st));
+		}
+		++layer_no;
+		return 0;
+	};
 	for (auto &Lp : _stack) {
 		const StackLayer &L = *Lp;
+		if (sp.parallel_block) {
+			ST_TRY(stack_layer_parallel(S, L, n, pos0, ctl, st));
+			ST_TRY(tap());
+			continue;
+		}
 		const yalm::MixerSpec &m = L.spec.mix;
 		const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, no = m.heads * m.vdim, ld = nq + nk + nv;
 		// ---- token mixer ----
@@ -464,9 +687,9 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 			}
 		} else if (f.kind == FfnSpec::Moe) {
 			ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.x, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
-			                             f.renormalize ? 1 : 0, st));
+			                             f.renormalize ? 1 : 0, f.renorm_eps, f.groups, f.keep_groups, st));
 			if (S.moe_gu && !from_ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
-				ST_TRY(stack_moe_grouped(S, L, n, act, st));
+				ST_TRY(stack_moe_grouped(S, L, S.x, n, act, st));
 			else {
 				ST_TRY(yalm_moe_glu_slots(S.h, S.x, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
 				                          f.weight_on_input ? 1 : 0, st));
@@ -474,12 +697,14 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 			}
 			ST_TRY(yalm_norm_residual_rows(S.x, S.y, W, f.top, L.norm2, woff, sp.norm_eps, n, W, st));
 		}
+		ST_TRY(tap());
 	}
 	if (n_want > 0) {
-		ST_TRY(yalm_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, woff, sp.norm_eps, n_want, W, st));
+		ST_TRY(yalm_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, sp.norm_scalar, woff, sp.norm_eps, n_want, W, st));
 		// a single wanted row lands directly where the samplers read it
 		float *dst = n_want == 1 ? s.logits_dev() : S.logits;
 		ST_TRY(stack_linear(*this, c, S.a16, dst, sp.vocab, S.xn, W, wcls, n_want, sp.vocab, W, sp.logit_scale, st));
+		if (sp.logit_softcap > 0.f) ST_TRY(yalm_softcap_rows(dst, n_want, sp.vocab, sp.logit_softcap, st));
 	}
 	return (int)cudaGetLastError();
 }

@@ -292,6 +292,9 @@ struct Model {
 	// layered models: per-layer taps for tests (which: 0 key ring, 1 value ring, 2 pooled keys, 3 pooled values -> fp32 copies)
 	int stack_read(int layer, int which, float *dst, size_t count);
 	int stack_ring_slots(int layer) const;
+	// Tests: after every layer of the next passes, the residual rows (n, width) are copied to dst + layer * n * width
+	// (host, n_layers * n * width floats for calls of n <= stack_chunk rows); null switches it off.
+	void stack_tap(float *dst) { _stack_tap = dst; }
 	size_t device_bytes() const { return _device_bytes; }
 	// loader facts for tests / bench: number of device allocations behind the model (1) and whether the upload went through pinned staging
 	int device_allocations() const { return _arena ? 1 : 0; }
@@ -320,18 +323,21 @@ private:
 	// ---- layered executor (stack.cpp) ----
 	friend struct yalm::StackLayer;
 	std::vector<std::shared_ptr<yalm::StackLayer>> _stack;
+	float *_embed_norm = nullptr;                   // weight of the norm after the embedding, when the design has one
 	void *_pos_table = nullptr;                     // learned positions (max_positions, dim), weight dtype
 	std::vector<std::vector<char>> _host_converted; // weights converted on the host (bf16 -> fp32, norm weights), alive until the upload
 	struct StackScratch;
 	std::shared_ptr<StackScratch> _scratch;
 	int _stack_pos = 0; // next position of the current sequence
+	float *_stack_tap = nullptr;
 	int _stack_step_nodes = 0; // kernel nodes of the captured decode step (pass + sampler), once a step has been captured
 	void build_stack(YALMData &data);
 	void cuda_stack(int device);
 	int stack_rows(InferenceState &s, const int *tokens, int n, int pos0, const int *want, int n_want, float *logits_out, const int *targets,
 	               float *probs_out);
 	int stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want);
-	int stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, int n, int act, cudaStream_t st);
+	int stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const float *x, int n, int act, cudaStream_t st);
+	int stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int n, int pos0, const int *ctl, cudaStream_t st);
 	int stack_generate(InferenceState &s, int token, int pos, int n_gen, float temperature, unsigned long long seed, int *tokens_out,
 	                   float *logits_out, float *device_ms);
 	Device _device = Device::CPU;
