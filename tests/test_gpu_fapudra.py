@@ -127,8 +127,9 @@ def test_short_convolution_in_portions(taps, sizes):
 
 
 # ---- the sigmoid attention alone -------------------------------------------------------------------------------------------
-def run_sigmoid_attention(q, k, rel, hb, gate, window, keep, scale, far, ring, sizes, cache_f32=1):
+def run_sigmoid_attention(q, k, rel, hb, gate, window, keep, scale, far, ring, sizes, cache_f32=1, mma=False):
     L = api.lib()
+    L.yalm_attn_sigmoid_mma.argtypes = [vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp]
     L.yalm_qk_bias_append_rows.argtypes = [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp]
     L.yalm_attn_sigmoid_rows.argtypes = [vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, vp, vp]
     L.yalm_attn_sigmoid_workspace.restype = C.c_size_t
@@ -147,6 +148,10 @@ def run_sigmoid_attention(q, k, rel, hb, gate, window, keep, scale, far, ring, s
     for at, n in portions(T, sizes):
         ok(L.yalm_qk_bias_append_rows(ptr(rows[at:]), vp(rows[at:].data_ptr() + 4 * H * d), ld, None, None, ptr(ringb), ptr(firstb), n, H, G, d, ring, kp,
                                       cache_f32, at, None, None), "qk_bias_append_rows")
+        if mma:
+            ok(L.yalm_attn_sigmoid_mma(ptr(out[at:]), H * d, ptr(rows[at:]), ld, ptr(ringb), ptr(firstb), ptr(gd[at:]) if gd is not None else None, H * d,
+                                       ptr(reld), ptr(bucket), ptr(hbd), n, H, G, d, ring, window, kp, scale, T, at, None, None), "attn_sigmoid_mma")
+            continue
         ok(L.yalm_attn_sigmoid_rows(ptr(out[at:]), H * d, ptr(rows[at:]), ld, ptr(ringb), ptr(firstb), ptr(gd[at:]) if gd is not None else None, H * d, ptr(reld),
                                     ptr(bucket), ptr(hbd), ptr(ws), n, H, G, d, ring, window, kp, scale, cache_f32, T, at, None, None), "attn_sigmoid_rows")
     return out.cpu().numpy().reshape(T, H, d)
@@ -212,6 +217,22 @@ def test_sigmoid_attention_over_a_bf16_ring():
     want = O.sigmoid_attention_core(q, kr, rel, hb, 11, 2, 1.0, far=20)
     got = run_sigmoid_attention(q, k, rel, hb, None, 11, 2, 1.0, 20, 24, [5, 1, 9], cache_f32=0)
     close_enough(got, want, 2e-2)
+
+
+@pytest.mark.parametrize("d,window,keep,sizes,ring", [(32, 9, 3, [1000], 240), (64, 70, 5, [64, 17, 100], 170), (128, 33, 40, [16, 130], 163), (64, 0, 0, [90, 16], 230),
+                                                      (64, 130, 0, [200], 330)])
+def test_sigmoid_attention_on_the_tensor_cores(d, window, keep, sizes, ring):
+    T, H, G = 230, 4, 2
+    q, k = crafted(T, H, G, d, window, keep, seed=d)
+    rng = np.random.default_rng(6)
+    rel, hb, gate = rng.standard_normal((12, H)), np.full(H, -20.0), rng.standard_normal((T, H, d))
+    kr = O.from_bf16_bits(O.to_bf16_bits(k.astype(np.float32))).reshape(k.shape).astype(np.float64)
+    qr = O.from_bf16_bits(O.to_bf16_bits(q.astype(np.float32))).reshape(q.shape).astype(np.float64)
+    want = O.sigmoid_attention_core(qr, kr, rel, hb, window, keep, 1.0, far=50) * O.sigmoid(gate)
+    got = run_sigmoid_attention(q, k, rel, hb, gate, window, keep, 1.0, 50, ring, sizes, cache_f32=0, mma=True)
+    close_enough(got, want, 1e-2)       # the weights are rounded to bf16 for the second product
+    if window:
+        assert np.abs(O.sigmoid_attention_core(qr, kr, rel, hb, window + 1, keep, 1.0, far=50) * O.sigmoid(gate) - want).max() > 0.3
 
 
 # ---- models --------------------------------------------------------------------------------------------------------------

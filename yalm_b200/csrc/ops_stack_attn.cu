@@ -12,6 +12,8 @@
 
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
 namespace yalm {
 namespace stack {
 
@@ -220,6 +222,164 @@ static int launch_mma(float *out, int ldo, const float *q, int ldq, const void *
 	return (int)cudaGetLastError();
 }
 
+
+// ---- sigmoid-weighted attention whose values are its keys, many rows, tensor cores ------------------------------------------
+// Same rule as ops_stack_state.cu's attn_sigmoid_rows_kernel (the route for decode-sized calls, the fp32 ring and other head
+// sizes): row i sees the positions lo(i) .. i from the ring and 0 .. min(keep, lo(i)) - 1 from the kept-first buffer, with
+// weight sigmoid(q . k * scale + rel[bucket[i - j], h] + hb[h]), not normalised; out = (sum of weight * key) * sigmoid(gate).
+// Same tiling as above, but one tile buffer pair serves both products (S = Q K^T reads the tile's rows, O += P K reads it
+// transposed), there is no running maximum or sum, and the distance bias of this head comes from a shared-memory table
+// over the distances the CTA meets inside the window (tb entries; farther ones, met only through kept tokens, are looked
+// up in global memory).
+template <int D>
+__global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                               const __nv_bfloat16 *__restrict__ ring_buf, const __nv_bfloat16 *__restrict__ first_buf,
+                                                               const float *__restrict__ gate, int ldg, const float *__restrict__ rel,
+                                                               const int *__restrict__ bucket, const float *__restrict__ hb, int n, int n_heads, int n_kv,
+                                                               int ring, int window, int keep, float scale, int tb, int pos0, const int *__restrict__ ctl) {
+	constexpr int LD = D + 8, KS = D / 16, OT = D / 8;
+	extern __shared__ __align__(16) __nv_bfloat16 smb[];
+	__nv_bfloat16 *Qs = smb, *Kbuf = Qs + 64 * LD;
+	float *relt = reinterpret_cast<float *>(Kbuf + 2 * 64 * LD);
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int h = blockIdx.y, g = h / (n_heads / n_kv), i0 = blockIdx.x * 64;
+	const int p0 = ctl ? ctl[CTL_POS] : pos0;
+	const __nv_bfloat16 *rbase = ring_buf + (size_t)g * ring * D, *fbase = first_buf ? first_buf + (size_t)g * keep * D : nullptr;
+	const float hbh = hb ? hb[h] : 0.f;
+	for (int c = threadIdx.x; c < 64 * (D / 4); c += 128) {
+		const int r = c / (D / 4), d = (c % (D / 4)) * 4;
+		float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+		if (i0 + r < n) v = *reinterpret_cast<const float4 *>(q + (size_t)(i0 + r) * ldq + (size_t)h * D + d);
+		uint2 pk;
+		pk.x = pack_bf2(v.x, v.y), pk.y = pack_bf2(v.z, v.w);
+		*reinterpret_cast<uint2 *>(Qs + r * LD + d) = pk;
+	}
+	const int i_first = p0 + i0, i_last = p0 + min(i0 + 63, n - 1);
+	auto lo_of = [&](int i) { return window > 0 ? max(0, i - window + 1) : 0; };
+	const int lo_min = lo_of(i_first);
+	const int nfirst_max = min(keep, lo_of(i_last));
+	for (int d = threadIdx.x; d < tb; d += 128) relt[d] = (rel && d <= i_last) ? rel[(size_t)bucket[d] * n_heads + h] + hbh : hbh;
+	__syncthreads();
+	auto bias_of = [&](int dist) { return dist < tb ? relt[dist] : (rel ? rel[(size_t)bucket[dist] * n_heads + h] + hbh : hbh); };
+	uint32_t qf[KS][4];
+	{
+		const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, cofs = (lane >> 4) * 8;
+#pragma unroll
+		for (int ks = 0; ks < KS; ++ks) ldsm_x4(qf[ks], (uint32_t)__cvta_generic_to_shared(Qs + r * LD + ks * 16 + cofs));
+	}
+	float o[OT][4];
+#pragma unroll
+	for (int t = 0; t < OT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+	const int rA = i0 + warp * 16 + (lane >> 2), rB = rA + 8;
+	const int iA = p0 + min(rA, n - 1), iB = p0 + min(rB, n - 1); // rows past n repeat the last valid row and are never stored
+	const int loA = lo_of(iA), loB = lo_of(iB), nfA = min(keep, loA), nfB = min(keep, loB);
+	const int first_tiles = (nfirst_max + 63) / 64, token_tiles = (i_last - lo_min) / 64 + 1;
+	const int n_tiles = first_tiles + token_tiles;
+	auto stage = [&](int tt) {
+		const bool first = tt < first_tiles;
+		const int base = first ? tt * 64 : lo_min + (tt - first_tiles) * 64;
+		__nv_bfloat16 *Ks = Kbuf + (tt & 1) * 64 * LD;
+		for (int c = threadIdx.x; c < 64 * (D / 8); c += 128) {
+			const int r = c / (D / 8), d = (c % (D / 8)) * 8;
+			if (first) {
+				const bool in = base + r < nfirst_max;
+				cp_async16(Ks + r * LD + d, fbase + (size_t)(in ? base + r : 0) * D + d, in);
+			} else {
+				const bool in = base + r <= i_last;
+				cp_async16(Ks + r * LD + d, rbase + (size_t)((in ? base + r : i_last) % ring) * D + d, in);
+			}
+		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	stage(0);
+	for (int tt = 0; tt < n_tiles; ++tt) {
+		const bool first = tt < first_tiles;
+		const int base = first ? tt * 64 : lo_min + (tt - first_tiles) * 64; // position of the tile's first key
+		const __nv_bfloat16 *Ks = Kbuf + (tt & 1) * 64 * LD;
+		__syncthreads();
+		if (tt + 1 < n_tiles) {
+			stage(tt + 1);
+			asm volatile("cp.async.wait_group 1;" ::: "memory");
+		} else
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
+		__syncthreads();
+		float s[8][4];
+#pragma unroll
+		for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+		{
+			const int kr = (lane & 7) + (lane >> 4) * 8, kcofs = ((lane >> 3) & 1) * 8;
+#pragma unroll
+			for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+				for (int t = 0; t < 8; t += 2) {
+					uint32_t b[4];
+					ldsm_x4(b, (uint32_t)__cvta_generic_to_shared(Ks + (t * 8 + kr) * LD + ks * 16 + kcofs));
+					mma_bf16(s[t], qf[ks], b[0], b[1]);
+					mma_bf16(s[t + 1], qf[ks], b[2], b[3]);
+				}
+		}
+		// ---- weights: an interval of positions per row, fp32 sigmoid ----
+		const int minA = first ? 0 : loA, maxA = first ? nfA - 1 : iA, minB = first ? 0 : loB, maxB = first ? nfB - 1 : iB;
+		uint32_t pf[4][4];
+#pragma unroll
+		for (int t = 0; t < 8; ++t) {
+			const int key = base + t * 8 + (lane & 3) * 2;
+			float w[4];
+#pragma unroll
+			for (int e = 0; e < 4; ++e) {
+				const int kk = key + (e & 1), lo = e < 2 ? minA : minB, hi = e < 2 ? maxA : maxB, i = e < 2 ? iA : iB;
+				w[e] = (kk >= lo && kk <= hi) ? 1.0f / (1.0f + expf(-(s[t][e] * scale + bias_of(i - kk)))) : 0.f;
+			}
+			pf[t >> 1][(t & 1) * 2] = pack_bf2(w[0], w[1]);
+			pf[t >> 1][(t & 1) * 2 + 1] = pack_bf2(w[2], w[3]);
+		}
+		// ---- O += P K ----
+		{
+			const int vr = (lane & 7) + ((lane >> 3) & 1) * 8, vcofs = (lane >> 4) * 8;
+#pragma unroll
+			for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+				for (int t = 0; t < OT; t += 2) {
+					uint32_t b[4];
+					ldsm_x4_t(b, (uint32_t)__cvta_generic_to_shared(Ks + (kk * 16 + vr) * LD + t * 8 + vcofs));
+					mma_bf16(o[t], pf[kk], b[0], b[1]);
+					mma_bf16(o[t + 1], pf[kk], b[2], b[3]);
+				}
+		}
+	}
+#pragma unroll
+	for (int t = 0; t < OT; ++t) {
+		const int d = h * D + t * 8 + (lane & 3) * 2;
+		if (rA < n) {
+			float2 gv = make_float2(1.f, 1.f);
+			if (gate) gv = make_float2(1.0f / (1.0f + expf(-gate[(size_t)rA * ldg + d])), 1.0f / (1.0f + expf(-gate[(size_t)rA * ldg + d + 1])));
+			*reinterpret_cast<float2 *>(out + (size_t)rA * ldo + d) = make_float2(o[t][0] * gv.x, o[t][1] * gv.y);
+		}
+		if (rB < n) {
+			float2 gv = make_float2(1.f, 1.f);
+			if (gate) gv = make_float2(1.0f / (1.0f + expf(-gate[(size_t)rB * ldg + d])), 1.0f / (1.0f + expf(-gate[(size_t)rB * ldg + d + 1])));
+			*reinterpret_cast<float2 *>(out + (size_t)rB * ldo + d) = make_float2(o[t][2] * gv.x, o[t][3] * gv.y);
+		}
+	}
+}
+
+template <int D>
+static int launch_sigmoid_mma(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
+                              const float *rel, const int *bucket, const float *hb, int n, int n_heads, int n_kv, int ring, int window, int keep, float scale,
+                              int context, int pos0, const int *ctl, cudaStream_t st) {
+	const int tb = std::min(4096, window > 0 ? window + 64 : std::max(64, context));
+	const size_t smem = sizeof(__nv_bfloat16) * (3 * 64 * (D + 8)) + sizeof(float) * tb;
+	static size_t configured = 0;
+	if (smem > 48 * 1024 && smem > configured) {
+		YALM_TRY(cudaFuncSetAttribute(attn_sigmoid_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+		configured = smem;
+	}
+	attn_sigmoid_mma_kernel<D><<<dim3((n + 63) / 64, n_heads), 128, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)ring_buf,
+	                                                                            (const __nv_bfloat16 *)first_buf, gate, ldg, rel, bucket, hb, n, n_heads, n_kv, ring,
+	                                                                            window, keep, scale, tb, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
 } // namespace stack
 } // namespace yalm
 
@@ -251,4 +411,23 @@ extern "C" int yalm_attn_window_pool_mma(float *out, int ldo, const float *q, in
 	MMA_CASE(128, 128);
 #undef MMA_CASE
 	return YALM_EINVAL;
+}
+
+// 1 when yalm_attn_sigmoid_mma has a kernel for this head size (bf16 ring only).
+extern "C" int yalm_attn_sigmoid_mma_shape(int dk) {
+	return dk == 32 || dk == 64 || dk == 128;
+}
+
+// The tensor-core route of yalm_attn_sigmoid_rows: bf16 ring and kept-first buffer, head sizes of yalm_attn_sigmoid_mma_shape,
+// q rows 16-byte aligned (ldq a multiple of 4 floats), out and gate rows 8-byte aligned.
+extern "C" int yalm_attn_sigmoid_mma(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
+                                     const float *rel, const int *bucket, const float *hb, int n, int n_heads, int n_kv, int dk, int ring, int window,
+                                     int keep, float scale, int context, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!out || !q || !ring_buf || n < 1 || n_kv < 1 || n_heads % n_kv || (keep > 0 && !first_buf) || (rel && !bucket) || ldq % 4 || ldo % 2 ||
+	    ((uintptr_t)q & 15) || ((uintptr_t)out & 7) || !yalm_attn_sigmoid_mma_shape(dk))
+		return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	if (dk == 32) return launch_sigmoid_mma<32>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
+	if (dk == 64) return launch_sigmoid_mma<64>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
+	return launch_sigmoid_mma<128>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
 }

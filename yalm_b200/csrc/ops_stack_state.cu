@@ -417,7 +417,7 @@ extern "C" int yalm_norm_shift_rows(float *h, float *hs, const float *x, const f
 
 extern "C" int yalm_conv_act_rows(float *out, int ldo, const float *in, int ldi, const float *w, const float *bias, float *state, int n, int channels,
                                   int taps, int pos0, const int *ctl, yalm_stream_t s) {
-	if (!out || !in || !w || !state || n < 1 || channels < 1 || taps < 1 || out == in) return YALM_EINVAL;
+	if (!out || !in || !w || (!state && taps > 1) || n < 1 || channels < 1 || taps < 1 || out == in) return YALM_EINVAL;
 	cudaStream_t st = (cudaStream_t)s;
 	const dim3 grid((channels + 127) / 128, (n + kConvRows - 1) / kConvRows);
 	conv_act_rows_kernel<<<grid, 128, 0, st>>>(out, ldo, in, ldi, w, bias, state, n, channels, taps, pos0, ctl);

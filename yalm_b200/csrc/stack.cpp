@@ -584,8 +584,13 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 		const int keep = m.window > 0 ? m.keep_first : 0;
 		ST_TRY(yalm_qk_bias_append_rows(P + L.o_q, P + L.o_k, ldp, L.qkb, L.qkb + nq, L.kring, L.kfirst, n, m.heads, m.kv_heads, m.dim, L.ring, keep, f32, pos0,
 		                                ctl, st));
-		ST_TRY(yalm_attn_sigmoid_rows(S.att, no, P + L.o_q, ldp, L.kring, L.kfirst, P + L.o_gate, ldp, L.rel, L.bucket, L.head_bias, S.attn_ws, n, m.heads,
-		                              m.kv_heads, m.dim, L.ring, m.window, keep, m.scale, f32, c.max_seq_len, pos0, ctl, st));
+		// many rows over the bf16 ring: tensor cores; decode-sized calls, the fp32 ring and other head sizes: the SIMT kernel
+		if (!f32 && n >= 16 && ldp % 4 == 0 && L.o_q % 4 == 0 && L.o_gate % 2 == 0 && no % 2 == 0 && yalm_attn_sigmoid_mma_shape(m.dim) && !attn_mma_off())
+			ST_TRY(yalm_attn_sigmoid_mma(S.att, no, P + L.o_q, ldp, L.kring, L.kfirst, P + L.o_gate, ldp, L.rel, L.bucket, L.head_bias, n, m.heads, m.kv_heads,
+			                             m.dim, L.ring, m.window, keep, m.scale, c.max_seq_len, pos0, ctl, st));
+		else
+			ST_TRY(yalm_attn_sigmoid_rows(S.att, no, P + L.o_q, ldp, L.kring, L.kfirst, P + L.o_gate, ldp, L.rel, L.bucket, L.head_bias, S.attn_ws, n, m.heads,
+			                              m.kv_heads, m.dim, L.ring, m.window, keep, m.scale, f32, c.max_seq_len, pos0, ctl, st));
 		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, no, L.wo, n, W, no, ls.left_scale, st));
 		// ---- right: gated delta rule ----
 		const yalm::DeltaSpec &d = ls.delta;
