@@ -47,6 +47,7 @@ WORKLOADS = {
     # batched prefill: a different metric (prompt tokens hydrated per second), its own line
     # the layered design at model-like sizes beside the equal-size .yalm block (yalm_b200/stack_bench.py): prefill and decode, one line
     "retezen-sizes": ("tiny", "bf16", 4096, "Retezen (windowed attention with pooled blocks, dense / routed feed-forward) at model-like sizes"),
+    "fapudra-sizes": ("tiny", "bf16", 4096, "Fapudra (parallel blocks: state-space / sigmoid attention + gated delta rule, routed experts) at model-like sizes"),
     "mistral-7b-fp16-prefill": ("mistral-7b", "fp16", 4096, "Mistral-7B-v0.2 fp16 random-init, 4096-token prompt hydrated in 512-token chunks (tcgen05 GEMMs)"),
 }
 HEADLINE = "mistral-7b-fp16-4k"
@@ -362,6 +363,11 @@ def main():
             raise SystemExit("bench.py: the layered models run on one GPU")
         from yalm_b200 import stack_bench
         return stack_bench.run(args, base, _emit, write_model, shm_path, ClockSampler)
+    if args.workload == "fapudra-sizes":
+        if world > 1:
+            raise SystemExit("bench.py: the layered models run on one GPU")
+        from yalm_b200 import stack_bench
+        return stack_bench.run_fapudra(args, base, _emit, shm_path, ClockSampler)
     if args.workload.endswith("-prefill"):
         if world > 1:
             raise SystemExit("bench.py: the prefill workload is single-GPU")

@@ -328,7 +328,8 @@ __global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(float *__restrict
 #pragma unroll
 			for (int e = 0; e < 4; ++e) {
 				const int kk = key + (e & 1), lo = e < 2 ? minA : minB, hi = e < 2 ? maxA : maxB, i = e < 2 ? iA : iB;
-				w[e] = (kk >= lo && kk <= hi) ? 1.0f / (1.0f + expf(-(s[t][e] * scale + bias_of(i - kk)))) : 0.f;
+				// fast exponential and reciprocal: the weight is rounded to bf16 as the operand of the second product
+				w[e] = (kk >= lo && kk <= hi) ? __fdividef(1.0f, 1.0f + __expf(-(s[t][e] * scale + bias_of(i - kk)))) : 0.f;
 			}
 			pf[t >> 1][(t & 1) * 2] = pack_bf2(w[0], w[1]);
 			pf[t >> 1][(t & 1) * 2 + 1] = pack_bf2(w[2], w[3]);

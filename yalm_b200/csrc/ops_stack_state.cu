@@ -106,9 +106,12 @@ __global__ void __launch_bounds__(128) conv_state_rows_kernel(const float *__res
 //   u = beta * (v - S^T k)   (delta rule)   or   u = vscale * v
 //   S <- S + k u^T;   o = S^T q  (+ skip * v)
 // One CTA owns 16 columns of one head; 8 neighbouring lanes share a column, lane `sub` holding the rows e * 8 + sub in
-// registers, so the two dot products of a step are EPL multiply-adds and three shuffles.  k, q, the decays and v of 8
-// positions are staged in shared memory at a time.  The order of every sum is fixed, so a position's output does not depend
-// on how the rows were cut into calls.  State in global memory: (head, column, row) fp32.
+// registers, so the two dot products of a step are EPL multiply-adds (four partial sums) and three shuffles.  k, q, the
+// decays and v of 8 positions at a time go global -> shared with cp.async into one of two stages: the next 8 load while
+// these are consumed.  The reduction of a position's output is carried into the next position's step, where it shares the
+// shuffle rounds of that step's S^T k, so only the recurrence itself (decay, S^T k, update) is a serial chain.  The order of
+// every sum is fixed, so a position's output does not depend on how the rows were cut into calls.  State in global memory:
+// (head, column, row) fp32.
 struct ScanArgs {
 	float *out;
 	int ldo;
@@ -118,14 +121,22 @@ struct ScanArgs {
 	float *state;
 	int n, H, rep, D, P, pos0;
 	const int *ctl;
+	int vec; // k, q and per-channel decay rows are 16-byte aligned: 16-byte copies
 };
 constexpr int kScanCols = 16, kScanTok = 8, kScanMaxD = 256;
 
+__device__ __forceinline__ void cp_async4(float *smem, const float *gmem) {
+	asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async16f(float *smem, const float *gmem) {
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+
 template <int EPL>
 __global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
-	constexpr int DP = EPL * 8;
-	__shared__ __align__(16) float ks[kScanTok * kScanMaxD], qs[kScanTok * kScanMaxD], gs[kScanTok * kScanMaxD];
-	__shared__ float vs[kScanTok][kScanCols], sc[kScanTok][3];
+	constexpr int DP = EPL * 8, TOK = kScanTok;
+	constexpr int STAGE = 3 * TOK * DP + TOK * kScanCols + TOK * 4; // k, q, decay rows; v; (decay, vscale, beta) per position
+	extern __shared__ __align__(16) float scan_sm[];
 	const int h = blockIdx.y, kh = h / a.rep, c0 = blockIdx.x * kScanCols;
 	const int tid = threadIdx.x, col = tid >> 3, sub = tid & 7;
 	const bool live = c0 + col < a.P;
@@ -135,56 +146,93 @@ __global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
 #pragma unroll
 	for (int e = 0; e < EPL; ++e) s[e] = (!fresh && e * 8 + sub < a.D) ? sp[e * 8 + sub] : 0.f;
 	const float skip = a.skip ? a.skip[h] : 0.f;
-	for (int t0 = 0; t0 < a.n; t0 += kScanTok) {
-		const int tc = min(kScanTok, a.n - t0);
-		__syncthreads(); // the previous positions have been consumed
-		for (int idx = tid; idx < tc * DP; idx += blockDim.x) {
-			const int t = idx / DP, i = idx % DP;
-			const bool in = i < a.D;
-			ks[idx] = in ? a.k[(size_t)(t0 + t) * a.ldk + kh * a.D + i] : 0.f;
-			qs[idx] = in ? a.q[(size_t)(t0 + t) * a.ldq + kh * a.D + i] : 0.f;
-			if (a.decay_per_channel) gs[idx] = in ? a.decay[(size_t)(t0 + t) * a.ldd + h * a.D + i] : 0.f;
+	// what the copies never write: rows past D, columns past P, and the defaults of absent per-position scalars
+	for (int idx = tid; idx < 2 * STAGE; idx += blockDim.x) {
+		const int r = idx % STAGE;
+		scan_sm[idx] = (r >= 3 * TOK * DP + TOK * kScanCols && (r - 3 * TOK * DP - TOK * kScanCols) % 4 < 2) ? 1.f : 0.f;
+	}
+	__syncthreads();
+	auto issue = [&](int t0, int stage) {
+		float *ks = scan_sm + stage * STAGE, *qs = ks + TOK * DP, *gs = qs + TOK * DP, *vs = gs + TOK * DP, *sc = vs + TOK * kScanCols;
+		const int tc = min(TOK, a.n - t0);
+		if (a.vec) {
+			const int D4 = a.D >> 2;
+			for (int idx = tid; idx < tc * D4; idx += blockDim.x) {
+				const int t = idx / D4, i = (idx % D4) * 4;
+				cp_async16f(ks + t * DP + i, a.k + (size_t)(t0 + t) * a.ldk + kh * a.D + i);
+				cp_async16f(qs + t * DP + i, a.q + (size_t)(t0 + t) * a.ldq + kh * a.D + i);
+				if (a.decay_per_channel) cp_async16f(gs + t * DP + i, a.decay + (size_t)(t0 + t) * a.ldd + h * a.D + i);
+			}
+		} else {
+			for (int idx = tid; idx < tc * a.D; idx += blockDim.x) {
+				const int t = idx / a.D, i = idx % a.D;
+				cp_async4(ks + t * DP + i, a.k + (size_t)(t0 + t) * a.ldk + kh * a.D + i);
+				cp_async4(qs + t * DP + i, a.q + (size_t)(t0 + t) * a.ldq + kh * a.D + i);
+				if (a.decay_per_channel) cp_async4(gs + t * DP + i, a.decay + (size_t)(t0 + t) * a.ldd + h * a.D + i);
+			}
 		}
 		for (int idx = tid; idx < tc * kScanCols; idx += blockDim.x) {
 			const int t = idx / kScanCols, c = idx % kScanCols;
-			vs[t][c] = c0 + c < a.P ? a.v[(size_t)(t0 + t) * a.ldv + h * a.P + c0 + c] : 0.f;
+			if (c0 + c < a.P) cp_async4(vs + idx, a.v + (size_t)(t0 + t) * a.ldv + h * a.P + c0 + c);
 		}
 		if (tid < tc) {
-			sc[tid][0] = a.decay_per_channel ? 1.f : a.decay[(size_t)(t0 + tid) * a.ldd + h];
-			sc[tid][1] = a.vscale ? a.vscale[(size_t)(t0 + tid) * a.ldvs + h] : 1.f;
-			sc[tid][2] = a.beta ? a.beta[(size_t)(t0 + tid) * a.ldb + h] : 0.f;
+			if (!a.decay_per_channel) cp_async4(sc + tid * 4, a.decay + (size_t)(t0 + tid) * a.ldd + h);
+			if (a.vscale) cp_async4(sc + tid * 4 + 1, a.vscale + (size_t)(t0 + tid) * a.ldvs + h);
+			if (a.beta) cp_async4(sc + tid * 4 + 2, a.beta + (size_t)(t0 + tid) * a.ldb + h);
 		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	float po = 0.f, pvv = 0.f; // the previous position's output: partial sum of this lane, and its v
+	float *pout = nullptr;
+	issue(0, 0);
+	for (int c = 0, t0 = 0; t0 < a.n; ++c, t0 += TOK) {
+		const int tc = min(TOK, a.n - t0);
+		if (t0 + TOK < a.n) {
+			issue(t0 + TOK, (c + 1) & 1);
+			asm volatile("cp.async.wait_group 1;" ::: "memory");
+		} else
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
 		__syncthreads();
+		const float *ks = scan_sm + (c & 1) * STAGE, *qs = ks + TOK * DP, *gs = qs + TOK * DP, *vs = gs + TOK * DP, *sc = vs + TOK * kScanCols;
 		for (int t = 0; t < tc; ++t) {
 			const float *kt = ks + t * DP + sub, *qt = qs + t * DP + sub, *gt = gs + t * DP + sub;
-			const float vv = vs[t][col];
+			const float vv = vs[t * kScanCols + col];
 			if (a.decay_per_channel) {
 #pragma unroll
 				for (int e = 0; e < EPL; ++e) s[e] *= gt[e * 8];
 			} else {
-				const float d = sc[t][0];
+				const float d = sc[t * 4];
 #pragma unroll
 				for (int e = 0; e < EPL; ++e) s[e] *= d;
 			}
 			float u;
 			if (a.beta) {
-				float dot = 0.f;
+				float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-				for (int e = 0; e < EPL; ++e) dot = fmaf(s[e], kt[e * 8], dot);
-				dot += __shfl_xor_sync(kFull, dot, 4), dot += __shfl_xor_sync(kFull, dot, 2), dot += __shfl_xor_sync(kFull, dot, 1);
-				u = sc[t][2] * (vv - dot);
-			} else
-				u = sc[t][1] * vv;
-			float o = 0.f;
+				for (int e = 0; e < EPL; ++e) d4[e & 3] = fmaf(s[e], kt[e * 8], d4[e & 3]);
+				float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+				dot += __shfl_xor_sync(kFull, dot, 4), po += __shfl_xor_sync(kFull, po, 4);
+				dot += __shfl_xor_sync(kFull, dot, 2), po += __shfl_xor_sync(kFull, po, 2);
+				dot += __shfl_xor_sync(kFull, dot, 1), po += __shfl_xor_sync(kFull, po, 1);
+				u = sc[t * 4 + 2] * (vv - dot);
+			} else {
+				po += __shfl_xor_sync(kFull, po, 4), po += __shfl_xor_sync(kFull, po, 2), po += __shfl_xor_sync(kFull, po, 1);
+				u = sc[t * 4 + 1] * vv;
+			}
+			if (pout && sub == 0 && live) *pout = po + skip * pvv;
+			float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
 			for (int e = 0; e < EPL; ++e) {
 				s[e] = fmaf(kt[e * 8], u, s[e]);
-				o = fmaf(s[e], qt[e * 8], o);
+				o4[e & 3] = fmaf(s[e], qt[e * 8], o4[e & 3]);
 			}
-			o += __shfl_xor_sync(kFull, o, 4), o += __shfl_xor_sync(kFull, o, 2), o += __shfl_xor_sync(kFull, o, 1);
-			if (sub == 0 && live) a.out[(size_t)(t0 + t) * a.ldo + h * a.P + c0 + col] = o + skip * vv;
+			po = (o4[0] + o4[1]) + (o4[2] + o4[3]), pvv = vv;
+			pout = a.out + (size_t)(t0 + t) * a.ldo + h * a.P + min(c0 + col, a.P - 1);
 		}
+		__syncthreads(); // this stage is consumed: the copies of the position group after next may land in it
 	}
+	po += __shfl_xor_sync(kFull, po, 4), po += __shfl_xor_sync(kFull, po, 2), po += __shfl_xor_sync(kFull, po, 1);
+	if (pout && sub == 0 && live) *pout = po + skip * pvv;
 	if (live) {
 #pragma unroll
 		for (int e = 0; e < EPL; ++e)
@@ -431,15 +479,28 @@ extern "C" int yalm_state_scan_rows(float *out, int ldo, const float *k, int ldk
                                     int ldd, int decay_per_channel, const float *vscale, int ldvs, const float *beta, int ldb, const float *skip,
                                     float *state, int n, int heads, int rep, int D, int P, int pos0, const int *ctl, yalm_stream_t s) {
 	if (!out || !k || !q || !v || !decay || !state || n < 1 || heads < 1 || rep < 1 || heads % rep || D < 1 || D > kScanMaxD || P < 1) return YALM_EINVAL;
-	ScanArgs a{out, ldo, k, q, v, decay, vscale, beta, skip, ldk, ldq, ldv, ldd, ldvs, ldb, decay_per_channel, state, n, heads, rep, D, P, pos0, ctl};
+	auto al = [](const float *p, int ld) { return ((uintptr_t)p & 15) == 0 && ld % 4 == 0; };
+	const int vec = D % 4 == 0 && al(k, ldk) && al(q, ldq) && (!decay_per_channel || al(decay, ldd));
+	ScanArgs a{out, ldo, k, q, v, decay, vscale, beta, skip, ldk, ldq, ldv, ldd, ldvs, ldb, decay_per_channel, state, n, heads, rep, D, P, pos0, ctl, vec};
 	const dim3 grid((P + kScanCols - 1) / kScanCols, heads);
 	cudaStream_t st = (cudaStream_t)s;
-	if (D <= 8) state_scan_kernel<1><<<grid, kScanCols * 8, 0, st>>>(a);
-	else if (D <= 16) state_scan_kernel<2><<<grid, kScanCols * 8, 0, st>>>(a);
-	else if (D <= 32) state_scan_kernel<4><<<grid, kScanCols * 8, 0, st>>>(a);
-	else if (D <= 64) state_scan_kernel<8><<<grid, kScanCols * 8, 0, st>>>(a);
-	else if (D <= 128) state_scan_kernel<16><<<grid, kScanCols * 8, 0, st>>>(a);
-	else state_scan_kernel<32><<<grid, kScanCols * 8, 0, st>>>(a);
+#define SCAN_CASE(EPL_)                                                                                                                      \
+	{                                                                                                                                        \
+		constexpr size_t smem = sizeof(float) * 2 * (3 * kScanTok * EPL_ * 8 + kScanTok * kScanCols + kScanTok * 4);                        \
+		static bool configured = false;                                                                                                      \
+		if (smem > 48 * 1024 && !configured) {                                                                                               \
+			YALM_TRY(cudaFuncSetAttribute(state_scan_kernel<EPL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
+			configured = true;                                                                                                               \
+		}                                                                                                                                    \
+		state_scan_kernel<EPL_><<<grid, kScanCols * 8, smem, st>>>(a);                                                                       \
+	}
+	if (D <= 8) SCAN_CASE(1)
+	else if (D <= 16) SCAN_CASE(2)
+	else if (D <= 32) SCAN_CASE(4)
+	else if (D <= 64) SCAN_CASE(8)
+	else if (D <= 128) SCAN_CASE(16)
+	else SCAN_CASE(32)
+#undef SCAN_CASE
 	return (int)cudaGetLastError();
 }
 

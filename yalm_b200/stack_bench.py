@@ -92,6 +92,165 @@ def retezen_numbers(z, kind):
     return params, 2 * params + kv, flop
 
 
+# ---- Fapudra ---------------------------------------------------------------------------------------------------------------
+# name: width; attention (left) heads / kv heads / head size / window / kept first tokens; delta rule (right) heads x (dim, vdim)
+# and low-rank size; state-space heads x vdim, state; experts; layer order (p = parallel mixer, s = state space)
+FAPUDRA_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, window=1024, keep=4, rheads=8, rdim=128, rvdim=128, rank=64, sheads=32, svdim=64, state=128,
+                  moe_ff=1024, experts=8, top=2, groups=4, keep_groups=2, order="pssp", vocab=32000),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=4, rheads=16, rdim=128, rvdim=128, rank=64, sheads=64, svdim=64, state=128,
+                  moe_ff=2048, experts=8, top=2, groups=4, keep_groups=2, order="pssp", vocab=32000),
+}
+
+
+def write_fapudra(folder, z, context):
+    """A checkpoint directory of the given size: matrices tiled from one random block, norm weights 1."""
+    os.makedirs(folder, exist_ok=True)
+    rng = np.random.default_rng(2)
+    block = _bf16(rng.standard_normal(1 << 22).astype(np.float32) * 0.02)
+    W, conv = z["width"], 4
+    mlp = {"kind": "moe", "expert": {"ff": z["moe_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep_groups"]}}}
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "bias_max": 512, "scale": z["dim"] ** -0.5,
+                              "mask": {"size": z["window"], "keep_first": z["keep"]}},
+                     "right": {"heads": z["rheads"], "kv_heads": z["rheads"], "dim": z["rdim"], "vdim": z["rvdim"], "conv": conv},
+                     "left_scale": 1.0, "right_scale": 1.0}}
+    ssm = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": z["sheads"], "vdim": z["svdim"], "state": z["state"], "groups": 1, "norm_groups": 1, "conv": conv}}
+    layers = [par if c == "p" else ssm for c in z["order"]]
+    cfg = {"architecture": "Fapudra", "width": W, "vocab": z["vocab"], "max_positions": context, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+           "logit_softcap": 30.0, "layers": layers}
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    shapes = {"embed": (z["vocab"], W), "pos": (context, W), "embed.norm": (), "final.norm": (), "head": (z["vocab"], W)}
+    for i, c in enumerate(z["order"]):
+        p = "l%d." % i
+        shapes.update({p + "norm1": (), p + "shift": (W,), p + "mlp.router": (z["experts"], W)})
+        for e in range(z["experts"]):
+            shapes.update({p + "mlp.e%d.gate" % e: (z["moe_ff"], W), p + "mlp.e%d.up" % e: (z["moe_ff"], W), p + "mlp.e%d.down" % e: (W, z["moe_ff"])})
+        if c == "p":
+            nq, nk = z["heads"] * z["dim"], z["kv_heads"] * z["dim"]
+            rk, rv, rg = z["rheads"] * z["rdim"], z["rheads"] * z["rvdim"], z["rheads"] * z["rdim"]
+            a, b = p + "mix.left.", p + "mix.right."
+            shapes.update({a + "q": (nq, W), a + "q.b": (nq,), a + "k": (nk, W), a + "k.b": (nk,), a + "rel": (32, z["heads"]), a + "pb": (z["heads"],),
+                           a + "g": (nq, W), a + "o": (W, nq),
+                           b + "q": (rk, W), b + "k": (rk, W), b + "v": (rv, W), b + "q.conv": (rk, conv), b + "k.conv": (rk, conv), b + "v.conv": (rv, conv),
+                           b + "b": (z["rheads"], W), b + "A_log": (z["rheads"],), b + "norm": (z["rvdim"],), b + "a1": (z["rank"], W), b + "a2": (rg, z["rank"]),
+                           b + "dt_bias": (rg,), b + "g1": (z["rank"], W), b + "g2": (rv, z["rank"]), b + "o": (W, rv)})
+        else:
+            inner, ch = z["sheads"] * z["svdim"], z["sheads"] * z["svdim"] + 2 * z["state"]
+            m = p + "mix."
+            shapes.update({m + "in": (2 * inner + 2 * z["state"] + z["sheads"], W), m + "conv": (ch, conv), m + "conv.b": (ch,), m + "dt_bias": (z["sheads"],),
+                           m + "A_log": (z["sheads"],), m + "D": (z["sheads"],), m + "norm": (inner,), m + "o": (W, inner)})
+    header, off = {}, 0
+    for name, shp in shapes.items():
+        n = int(np.prod(shp)) if shp else 1
+        header[name] = {"dtype": "BF16", "shape": list(shp), "data_offsets": [off, off + 2 * n]}
+        off += 2 * n
+    h = json.dumps(header).encode()
+    h += b" " * (-len(h) % 8)
+    one = _bf16(np.ones(1, np.float32))[0]
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h)
+        for k, (name, shp) in enumerate(shapes.items()):
+            n = int(np.prod(shp)) if shp else 1
+            if not shp or name.endswith(".norm"):
+                f.write(np.full(n, one, np.uint16).tobytes())
+            elif len(shp) < 2:
+                f.write(block[:n].tobytes())
+            else:
+                f.write(np.resize(np.roll(block, 7919 * k), n).tobytes())
+    return cfg
+
+
+def fapudra_numbers(z):
+    """-> (decode bytes per token at CONTEXT, prefill FLOP per token): the active matrices once (bf16), the fp32 matrix states read
+    and written, the window of keys; 2 FLOP per active parameter plus the attention's and the recurrences' own products."""
+    W = z["width"]
+    experts = z["top"] * 3 * z["moe_ff"] * W + z["experts"] * W
+    params, state, extra = z["vocab"] * W, 0, 0.0
+    for c in z["order"]:
+        if c == "p":
+            nq, nk = z["heads"] * z["dim"], z["kv_heads"] * z["dim"]
+            rk, rv = z["rheads"] * z["rdim"], z["rheads"] * z["rvdim"]
+            params += (3 * nq + nk) * W + (2 * rk + 2 * rv + z["rheads"] + 2 * z["rank"]) * W + z["rank"] * (rk + rv) + experts
+            seen = min(CONTEXT, z["window"]) + z["keep"]
+            state += seen * nk * 2 + 2 * 4 * z["rheads"] * z["rdim"] * z["rvdim"]
+            extra += 4.0 * nq * seen + 8.0 * z["rheads"] * z["rdim"] * z["rvdim"]
+        else:
+            inner = z["sheads"] * z["svdim"]
+            params += (3 * inner + 2 * z["state"] + z["sheads"]) * W + experts
+            state += 2 * 4 * inner * z["state"]
+            extra += 6.0 * inner * z["state"]
+    return 2 * params + state, 2.0 * (params - z["vocab"] * W) + extra
+
+
+def run_fapudra(args, base, emit, shm_path, ClockSampler):
+    """`bench.py --workload fapudra-sizes`: the Fapudra design beside the closest existing model on the same executor, Retezen
+    with routed experts, at equal width, heads, window, experts, layers and vocabulary."""
+    import torch
+    from yalm_b200 import api
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(pk)) if os.path.exists(pk) else {"hbm_gbs": 6650.0, "bf16_tflops_sustained": 1400.0}
+    hbm, tflops = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops_sustained"])
+    steps = max(8, min(args.steps, 128))
+    clocks = ClockSampler(0)
+    clocks.start()
+    out, launches = [], 0
+
+    def measure(model, ids):
+        st = api.InferenceState(model)
+        st.forward_batch(ids[:1024], 0)                     # warm-up (sizes kernels, first-use set-up)
+        st.end_sequence()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        st.forward_batch(ids[:-1], 0)
+        t_pre = time.perf_counter() - t0
+        st.generate_greedy(ids[-1], CONTEXT - 1, max(3, args.warmup))   # first step eager + graph capture, untimed
+        st.generate_greedy(ids[0], CONTEXT - 1 + max(3, args.warmup), steps)
+        t_dec = st.device_ms / 1e3
+        n = model.launches()
+        st.close()
+        return (CONTEXT - 1) / t_pre, steps / t_dec, n
+
+    for name, z in FAPUDRA_SIZES.items():
+        ids = [(i * 7919 + 1) % z["vocab"] for i in range(CONTEXT)]
+        row = {"size": name, "width": z["width"], "layers": z["order"], "context": CONTEXT, "window": z["window"]}
+        folder = shm_path("yalm_bench_fapudra_%s_%d" % (name, os.getpid()))
+        try:
+            write_fapudra(folder, z, CONTEXT + steps + args.warmup + 8)
+            model = api.Model(folder, 0, api.BF16).cuda(0)
+        finally:
+            shutil.rmtree(folder, ignore_errors=True)
+        pre, dec, n = measure(model, ids)
+        model.close()
+        dec_bytes, pre_flop = fapudra_numbers(z)
+        launches += steps * n
+        row["fapudra"] = {"prefill_tok_s": pre, "decode_tok_s": dec, "prefill_frac_of_measured_bf16": pre_flop * pre / 1e12 / tflops,
+                          "decode_frac_of_measured_hbm": dec_bytes * dec / 1e9 / hbm, "decode_bytes_per_token": dec_bytes, "launches_per_token": n}
+        zr = dict(z, pool=64, ff=0, layers=len(z["order"]))
+        folder = shm_path("yalm_bench_retezen_%s_%d" % (name, os.getpid()))
+        try:
+            write_retezen(folder, zr, "moe", CONTEXT + steps + args.warmup + 8)
+            model = api.Model(folder, 0, api.BF16).cuda(0)
+        finally:
+            shutil.rmtree(folder, ignore_errors=True)
+        pre, dec, n = measure(model, ids)
+        model.close()
+        _, r_bytes, r_flop = retezen_numbers(zr, "moe")
+        row["equal_size_retezen"] = {"prefill_tok_s": pre, "decode_tok_s": dec, "prefill_frac_of_measured_bf16": r_flop * pre / 1e12 / tflops,
+                                     "decode_frac_of_measured_hbm": r_bytes * dec / 1e9 / hbm, "decode_bytes_per_token": r_bytes, "launches_per_token": n}
+        out.append(row)
+    clk = clocks.stop()
+    first = out[0]["fapudra"]
+    emit(dict(base, impl="ours", metric="batch-1 decode tok/s (Fapudra, first size; all sizes under `sizes`)", value=first["decode_tok_s"], steps=steps,
+              ms_per_step=1000.0 / first["decode_tok_s"], dtype="bf16", clocks=clk, gpu_launches=launches, sizes=out,
+              e2e={"value": first["decode_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
+                   "note": "device loop: token ids stay on the device, 4 bytes per token come back"},
+              config=dict(base["config"], workload="Fapudra at model-like sizes beside the equal-size Retezen stack", context=CONTEXT,
+                          l2="inputs larger than L2 (weights streamed per token)")))
+
+
 def run(args, base, emit, write_yalm, shm_path, ClockSampler):
     import torch
     from yalm_b200 import api
