@@ -251,6 +251,13 @@ int yalm_gemv_qkv_post(float *qkv, const float *x, const void *w, int n, int dty
                        float eps, int cache_f32, float *key_pool, float *value_pool, int pool, int max_blocks, int pos0, const int *ctl,
                        unsigned *counter, yalm_stream_t s);
 
+/* yalm_gemv_norm_shift: yalm_norm_shift_rows for one row + the product of its shifted output, as one launch (h left in h_out
+ * and in the state).  yalm_gemv_residual_sum: y = alpha W x, then res += (y + add1) + sum_j slots[j] (yalm_residual_sum_rows). */
+int yalm_gemv_norm_shift(float *out, const float *x, const void *w, int n, int d, int dtype, const float *hw, int scalar_weight, float w_offset,
+                         float eps, const float *shift, float *state, float *h_out, int pos0, const int *ctl, unsigned *counter, yalm_stream_t s);
+int yalm_gemv_residual_sum(float *res, float *y, const float *x, const void *w, float alpha, int n, int d, int dtype, const float *add1,
+                           const float *slots, int nslots, int ldslots, unsigned *counter, yalm_stream_t s);
+
 /* ---- layers with per-sequence state besides a key / value ring (csrc/ops_stack_state.cu) ----
  * A call whose first position is 0 starts a sequence: stored state is taken as zero.  All state is fp32.
  * yalm_norm_shift_rows: h = rms(x) (w_offset + w), w one number if scalar_weight; hs (optional) = h + (h of the previous

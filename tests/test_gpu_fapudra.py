@@ -333,6 +333,26 @@ def test_whole_prompt_decoding_and_portions_agree_with_the_oracle(tmp_path, stor
     close(m, s)
 
 
+def test_decode_rows_with_the_block_fusions(tmp_path, monkeypatch):
+    """Norm + token shift inside the projection's launch, the residual add as the tail of the block's last product."""
+    monkeypatch.setenv("YALM_STACK_FUSE_BLOCK", "1")
+    cfg = O.make_config(width=64, layers=[O.parallel_layer(dim=16, rdim=16, rvdim=16, mlp=O.moe()), O.mamba2_layer(vdim=16, mlp=None),
+                                          O.mamba2_layer(vdim=16, mlp=O.moe(ff=16, experts=4, top=3, groups=2, keep=2))])
+    folder, W = checkpoint(tmp_path, cfg, seed=12)
+    T = 70
+    toks = tokens_for(cfg, T)
+    want = O.forward(cfg, W, toks)
+    for dtype, tol in ((api.F32, F32_TOL), (api.BF16, 3e-2)):
+        m, s = open_model(folder, dtype)
+        s.forward_rows(toks[:9], 0, [])
+        one = np.concatenate([s.forward_rows(toks[i:i + 1], i, [0]) for i in range(9, T)])
+        s.end_sequence()
+        first = np.concatenate([s.forward_rows(toks[i:i + 1], i, [0]) for i in range(5)])      # a sequence that starts with single rows
+        close(m, s)
+        close_enough(one, want[9:], tol)
+        close_enough(first, want[:5], tol)
+
+
 def test_state_given_back_and_used_again(tmp_path):
     cfg = four_layers()
     folder, W = checkpoint(tmp_path, cfg, seed=8)

@@ -105,6 +105,19 @@ size_t Config::active_bytes(size_t pos) const {
 		size_t total = 2 * W * ws + (size_t)s.vocab * W * ws + W * 4;
 		for (const yalm::LayerSpec &l : s.layers) {
 			const yalm::MixerSpec &m = l.mix;
+			if (s.parallel_block) {
+				// the packed projection and the output projection(s), the fp32 matrix state read and written, the window of keys
+				total += ((size_t)l.proj_width() + l.mixed_width()) * W * ws + 2 * W * 4;
+				if (l.kind == yalm::MixerKind::StateSpace) total += (size_t)2 * 4 * l.ssm.inner() * l.ssm.state;
+				else {
+					const yalm::DeltaSpec &d = l.delta;
+					total += ((size_t)d.decay_rank * d.heads * d.dim + (size_t)d.gate_rank * d.heads * d.vdim) * ws + (size_t)2 * 4 * d.heads * d.dim * d.vdim;
+					const size_t seen = (m.window > 0 ? std::min<size_t>(pos + 1, m.window) : pos + 1) + (m.window > 0 ? std::min<size_t>(m.keep_first, pos + 1) : 0);
+					total += seen * m.kv_heads * m.dim * cb;
+				}
+				if (l.ffn.kind == yalm::FfnSpec::Moe) total += ((size_t)l.ffn.experts * W + (size_t)l.ffn.top * 3 * l.ffn.ff * W) * ws;
+				continue;
+			}
 			const size_t nq = (size_t)m.heads * m.dim, nk = (size_t)m.kv_heads * m.dim, nv = (size_t)m.kv_heads * m.vdim, no = (size_t)m.heads * m.vdim;
 			total += (nq + nk + nv + no) * W * ws + (nq + nk + 2 * W) * 4;
 			const size_t seen = m.window > 0 ? std::min<size_t>(pos + 1, m.window) : pos + 1;
@@ -818,7 +831,12 @@ int Model::launches_per_forward(InferenceMode mode) const {
 	if (config->stack && _stack_step_nodes > 0) return _stack_step_nodes; // counted from the captured decode step
 	if (config->stack) { // before any capture, the per-op route: embed + per layer: qkv, q/k norm + append, [pool], attention, wo, norm + residual, feed-forward (4) [+ final norm, head]
 		int n = 1;
-		for (const yalm::LayerSpec &l : config->stack->layers) n += 5 + (l.mix.pool > 0 ? 1 : 0) + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 4);
+		for (const yalm::LayerSpec &l : config->stack->layers) {
+			if (config->stack->parallel_block) // norm + shift, projection, mixer (state space 5, parallel 14), experts 3, residual
+				n += 3 + (l.kind == yalm::MixerKind::StateSpace ? 5 : 14) + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 3);
+			else
+				n += 5 + (l.mix.pool > 0 ? 1 : 0) + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 4);
+		}
 		return n + (mode == InferenceMode::OUTPUT_LOGITS ? 2 : 0);
 	}
 	if (_mega_ok) return 1;

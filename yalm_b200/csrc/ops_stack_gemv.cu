@@ -2,10 +2,14 @@
 //
 // The product itself is the .yalm decode path's streaming GEMV (gemv.cuh: x staged in shared memory, every warp owns four
 // output rows with sixteen 16-byte weight loads in flight per lane, persistent grid).  Around it:
-//   head   the input may be a gated activation of a (gate | up) row: x[f] = act(g[f]) * (u[f] + offset), applied while staging
+//   head   the input may be a gated activation of a (gate | up) row: x[f] = act(g[f]) * (u[f] + offset), applied while staging;
+//          or the token-shifted norm of a residual row: h = rms(x) w, input = h + (previous position's h - h) * mu, every CTA
+//          recomputing the row's mean square, CTA 0 leaving h for the other sublayer
 //   tail   the CTA that finishes last (a ticket from one atomic counter, after a device-scope fence) runs, on the complete
 //          output vector, either the sublayer's output norm + residual add (x += rms(y) (offset + w)) or the q / k norm, value
-//          blending, cache append and — when this position completes a block — the block's mean key / value.
+//          blending, cache append and — when this position completes a block — the block's mean key / value; or the hand-over
+//          of the row's h to the token-shift state (once every CTA has read the old one); or the residual add of a parallel
+//          block, x += (this output + another sublayer's) + the selected experts' outputs.
 // One launch instead of two to four, on the path where launches, not bytes, are the larger cost.
 #include "common.cuh"
 
@@ -42,6 +46,15 @@ struct GemvTailArgs {
 	int vmode, nq, nk, nv, dk, dv, ring, pool, max_blocks, n_kv, cache_f32;
 	int pos0;
 	const int *ctl;
+	// head 2 (norm + token shift): x is the residual row; hw its norm weight (one number if hscalar); mu the shift weight;
+	// hstate the previous position's h (zero at position 0); hout receives this row's h.  Tail 3 then moves hout to hstate.
+	int head, hscalar;
+	const float *hw, *mu;
+	float hwoff, heps;
+	float *hstate, *hout;
+	// tail 4: res += (out + add1) + sum_{j < nslots} slots[j * ldslots + .]
+	const float *add1, *slots;
+	int nslots, ldslots;
 };
 
 // R rows per warp, 16 / R chunks of each in flight: few output rows (d below the warps the GPU holds) take fewer rows per
@@ -63,6 +76,26 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_tail_kernel(GemvTailArgs a)
 			v.x = glu_value(g.x, u.x, a.act, a.act_alpha, a.limit, a.up_offset), v.y = glu_value(g.y, u.y, a.act, a.act_alpha, a.limit, a.up_offset);
 			v.z = glu_value(g.z, u.z, a.act, a.act_alpha, a.limit, a.up_offset), v.w = glu_value(g.w, u.w, a.act, a.act_alpha, a.limit, a.up_offset);
 			*reinterpret_cast<float4 *>(xs + xs_slot<EP>(e)) = v;
+		}
+	} else if (a.head == 2) {
+		float ss = 0.f;
+		for (int e = threadIdx.x * 4; e < a.n; e += blockDim.x * 4) {
+			const float4 v = *reinterpret_cast<const float4 *>(a.x + e);
+			ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+		}
+		ss = block_sum(ss, red);
+		const float r = 1.0f / sqrtf(ss / a.n + a.heps);
+		const bool start = first_pos(a.ctl, a.pos0) == 0;
+		for (int e = threadIdx.x * 4; e < a.n; e += blockDim.x * 4) {
+			const float4 v = *reinterpret_cast<const float4 *>(a.x + e), m = *reinterpret_cast<const float4 *>(a.mu + e);
+			const float4 pv = start ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4 *>(a.hstate + e);
+			float4 g;
+			if (a.hscalar) g.x = g.y = g.z = g.w = a.hwoff + a.hw[0];
+			else g = make_float4(a.hwoff + a.hw[e], a.hwoff + a.hw[e + 1], a.hwoff + a.hw[e + 2], a.hwoff + a.hw[e + 3]);
+			const float4 h = make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w);
+			const float4 o = make_float4(h.x + (pv.x - h.x) * m.x, h.y + (pv.y - h.y) * m.y, h.z + (pv.z - h.z) * m.z, h.w + (pv.w - h.w) * m.w);
+			*reinterpret_cast<float4 *>(xs + xs_slot<EP>(e)) = o;
+			if (blockIdx.x == 0) *reinterpret_cast<float4 *>(a.hout + e) = h;
 		}
 	} else
 		stage_x_plain<EP>(xs, a.x, a.n);
@@ -88,6 +121,15 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_tail_kernel(GemvTailArgs a)
 	__threadfence();
 	if (a.tail == 1) {
 		norm_residual_row(a.res, a.out, 0, 1, a.nw, a.woff, a.eps, a.d, xs, red); // xs: free now, sized for max(n, d) by the launcher
+	} else if (a.tail == 3) { // every CTA has staged its input from the old state
+		for (int e = threadIdx.x; e < a.n; e += blockDim.x) a.hstate[e] = __ldcg(a.hout + e);
+	} else if (a.tail == 4) {
+		for (int e = threadIdx.x; e < a.d; e += blockDim.x) {
+			const float v = a.add1 ? a.add1[e] + __ldcg(a.out + e) : __ldcg(a.out + e);
+			float f = 0.f;
+			for (int j = 0; j < a.nslots; ++j) f += a.slots[(size_t)j * a.ldslots + e];
+			a.res[e] += v + f;
+		}
 	} else {
 		const int p = first_pos(a.ctl, a.pos0), slot = p % a.ring;
 		if (a.cache_f32) qkv_post_row<float>(a.out, (float *)a.kring, (float *)a.vring, a.vfirst, a.qnorm, a.knorm, a.vmix, a.vmode, a.nq, a.nk, a.nv, a.dk, a.dv, a.ring, slot, a.eps, red);
@@ -185,5 +227,30 @@ extern "C" int yalm_gemv_qkv_post(float *qkv, const float *x, const void *w, int
 		if (!rc && pool > 0) rc = yalm_kv_pool_rows(key_pool, value_pool, key_ring, value_ring, 1, n_kv, dk, dv, ring, pool, max_blocks, cache_f32, pos0, ctl, s);
 		return rc;
 	}
+	return launch_tail(a, dtype, (cudaStream_t)s);
+}
+
+// One decode row of a parallel block's mixer input: out (d) = W (d, n) hs with h = rms(x) (w_offset + hw) (hw one number if
+// scalar_weight), hs = h + (state - h) * shift (state: the previous position's h, zero at position 0); h is left in h_out
+// and becomes the state.  yalm_norm_shift_rows + the product, as one launch.
+extern "C" int yalm_gemv_norm_shift(float *out, const float *x, const void *w, int n, int d, int dtype, const float *hw, int scalar_weight, float w_offset,
+                                    float eps, const float *shift, float *state, float *h_out, int pos0, const int *ctl, unsigned *counter, yalm_stream_t s) {
+	if (!hw || !shift || !state || !h_out || ((uintptr_t)shift & 15) || ((uintptr_t)state & 15) || ((uintptr_t)h_out & 15) || (!scalar_weight && ((uintptr_t)hw & 15)))
+		return YALM_EINVAL;
+	GemvTailArgs a{};
+	a.out = out, a.x = x, a.w = (const char *)w, a.n = n, a.d = d, a.alpha = 1.f;
+	a.head = 2, a.hw = hw, a.hscalar = scalar_weight, a.hwoff = w_offset, a.heps = eps, a.mu = shift, a.hstate = state, a.hout = h_out;
+	a.tail = 3, a.counter = counter, a.pos0 = pos0, a.ctl = ctl;
+	return launch_tail(a, dtype, (cudaStream_t)s);
+}
+
+// The last product of a parallel block's decode row with the block's residual add as its tail: y = alpha W x, then
+// res += (y + add1) + sum_{j < nslots} slots[j] (add1: another sublayer's output or null; slots: the selected experts' outputs).
+extern "C" int yalm_gemv_residual_sum(float *res, float *y, const float *x, const void *w, float alpha, int n, int d, int dtype, const float *add1,
+                                      const float *slots, int nslots, int ldslots, unsigned *counter, yalm_stream_t s) {
+	if (!res || nslots < 0 || (nslots && !slots)) return YALM_EINVAL;
+	GemvTailArgs a{};
+	a.out = y, a.x = x, a.w = (const char *)w, a.n = n, a.d = d, a.alpha = alpha;
+	a.tail = 4, a.counter = counter, a.res = res, a.add1 = add1, a.slots = slots, a.nslots = nslots, a.ldslots = ldslots;
 	return launch_tail(a, dtype, (cudaStream_t)s);
 }

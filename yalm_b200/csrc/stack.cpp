@@ -499,6 +499,15 @@ static bool gemv_fusable(const Config &c, int n, int K, const void *w, const voi
 	return !off && n == 1 && K % 8 == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0 && (size_t)K * dtype_size(c.weight_dtype) % 16 == 0;
 }
 
+// YALM_STACK_FUSE_BLOCK=1: a parallel block's decode row runs norm + token shift inside its projection's launch and the
+// residual add as the tail of its last product.  Off by default: on B200 both measure 2 - 4 % slower per token than the two
+// small launches they save (every CTA of the projection recomputes the row's mean square, and the last-CTA ticket costs a
+// device-scope fence), inside the captured decode step.
+static bool block_fuse_on() {
+	const char *e = getenv("YALM_STACK_FUSE_BLOCK");
+	return e && e[0] == '1';
+}
+
 static bool attn_mma_off() { // YALM_STACK_ATTN_MMA=0: A/B against the SIMT kernel
 	static const bool off = [] { const char *e = getenv("YALM_STACK_ATTN_MMA"); return e && e[0] == '0'; }();
 	return off;
@@ -562,11 +571,31 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 	const yalm::LayerSpec &ls = L.spec;
 	const int dt = static_cast<int>(c.weight_dtype), W = sp.width, f32 = c.weight_dtype == DType::F32;
 	const float woff = sp.norm_one_plus ? 1.f : 0.f;
-	ST_TRY(yalm_norm_shift_rows(S.xn, sp.token_shift ? S.hs : nullptr, S.x, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, n, W, pos0, ctl, st));
-	const float *hin = sp.token_shift ? S.hs : S.xn;
 	const int ldp = ls.proj_width();
 	float *P = S.qkv;
-	ST_TRY(stack_linear(*this, c, S.a16, P, ldp, hin, W, L.wproj, n, ldp, W, 1.f, st));
+	const bool fuse = n == 1 && block_fuse_on();
+	if (fuse && sp.token_shift && gemv_fusable(c, n, W, L.wproj, S.x)) // a decode row: norm, shift and projection as one launch
+		ST_TRY(yalm_gemv_norm_shift(P, S.x, L.wproj, W, ldp, dt, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, S.xn, pos0, ctl, S.ticket, st));
+	else {
+		ST_TRY(yalm_norm_shift_rows(S.xn, sp.token_shift ? S.hs : nullptr, S.x, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, n, W, pos0, ctl, st));
+		ST_TRY(stack_linear(*this, c, S.a16, P, ldp, sp.token_shift ? S.hs : S.xn, W, L.wproj, n, ldp, W, 1.f, st));
+	}
+	// ---- experts on h (before the mixer, whose last product then carries the block's residual add on decode rows) ----
+	const FfnSpec &f = ls.ffn;
+	int nsum = 0;
+	if (f.kind == FfnSpec::Moe) {
+		const int act = f.act == yalm::GluAct::SigmoidScaled ? 2 : f.act == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
+		ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.xn, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
+		                             f.renormalize ? 1 : 0, f.renorm_eps, f.groups, f.keep_groups, st));
+		if (S.moe_gu && !ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
+			ST_TRY(stack_moe_grouped(S, L, S.xn, n, act, st));
+		else {
+			ST_TRY(yalm_moe_glu_slots(S.h, S.xn, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
+			                          f.weight_on_input ? 1 : 0, st));
+			ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
+		}
+		nsum = f.top;
+	}
 	const float *mix_b = nullptr;
 	if (ls.kind == yalm::MixerKind::StateSpace) {
 		const yalm::SsmSpec &q = ls.ssm;
@@ -576,6 +605,7 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 		ST_TRY(yalm_state_scan_rows(S.scan, inner, S.conv + inner, C, S.conv + inner + gn, C, S.conv, C, S.aux, q.heads, 0, P + o_dt, ldp, nullptr, 0, L.skip,
 		                            L.scan_state, n, q.heads, q.heads / q.groups, q.state, q.vdim, pos0, ctl, st));
 		ST_TRY(yalm_gated_group_norm_rows(S.att, inner, S.scan, inner, P, ldp, L.mix_norm, n, inner, q.norm_groups, sp.norm_eps, st));
+		if (fuse && gemv_fusable(c, n, inner, L.wout, S.att)) return yalm_gemv_residual_sum(S.x, S.y1, S.att, L.wout, 1.f, inner, W, dt, nullptr, S.y, nsum, W, S.ticket, st);
 		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, inner, L.wout, n, W, inner, 1.f, st));
 	} else {
 		// ---- left: sigmoid attention over the key ring and the kept first tokens ----
@@ -603,24 +633,9 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 		ST_TRY(yalm_state_scan_rows(S.scan, dv, S.conv + dk, C, S.conv, C, S.conv + 2 * dk, C, S.aux, lda, 1, nullptr, 0, P + L.o_beta, ldp, nullptr,
 		                            L.scan_state, n, d.heads, d.heads / d.kv_heads, d.dim, d.vdim, pos0, ctl, st));
 		ST_TRY(yalm_head_norm_gate_rows(S.att2, dv, S.scan, dv, S.aux + dg, lda, L.d_norm, n, d.heads, d.vdim, sp.norm_eps, st));
+		if (fuse && gemv_fusable(c, n, dv, L.wout, S.att2)) return yalm_gemv_residual_sum(S.x, S.y2, S.att2, L.wout, ls.right_scale, dv, W, dt, S.y1, S.y, nsum, W, S.ticket, st);
 		ST_TRY(stack_linear(*this, c, S.a16, S.y2, W, S.att2, dv, L.wout, n, W, dv, ls.right_scale, st));
 		mix_b = S.y2;
-	}
-	// ---- experts on h ----
-	const FfnSpec &f = ls.ffn;
-	int nsum = 0;
-	if (f.kind == FfnSpec::Moe) {
-		const int act = f.act == yalm::GluAct::SigmoidScaled ? 2 : f.act == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
-		ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.xn, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
-		                             f.renormalize ? 1 : 0, f.renorm_eps, f.groups, f.keep_groups, st));
-		if (S.moe_gu && !ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
-			ST_TRY(stack_moe_grouped(S, L, S.xn, n, act, st));
-		else {
-			ST_TRY(yalm_moe_glu_slots(S.h, S.xn, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
-			                          f.weight_on_input ? 1 : 0, st));
-			ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
-		}
-		nsum = f.top;
 	}
 	return yalm_residual_sum_rows(S.x, S.y1, mix_b, S.y, W, nsum, n, W, st);
 }
