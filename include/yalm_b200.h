@@ -299,11 +299,12 @@ int yalm_attn_sigmoid_rows(float *out, int ldo, const float *q, int ldq, const v
                            const float *rel, const int *bucket, const float *hb, float *workspace, int n, int n_heads, int n_kv, int dk, int ring,
                            int window, int keep, float scale, int cache_f32, int context, int pos0, const int *ctl, yalm_stream_t s);
 /* The same attention for many rows over a bf16 ring on the tensor cores (mma.sync bf16, fp32 scores and sigmoid): head sizes
- * 32, 64, 128 (yalm_attn_sigmoid_mma_shape), ldq % 4 == 0, ldo % 2 == 0. */
+ * 32, 64, 128 (yalm_attn_sigmoid_mma_shape), ldq % 4 == 0, ldo % 2 == 0.  table (optional, (n_heads, ldt)): rel[bucket[d], h] + hb[h]
+ * per head and distance, read instead of rel / bucket / hb. */
 int yalm_attn_sigmoid_mma_shape(int dk);
 int yalm_attn_sigmoid_mma(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
-                          const float *rel, const int *bucket, const float *hb, int n, int n_heads, int n_kv, int dk, int ring, int window, int keep,
-                          float scale, int context, int pos0, const int *ctl, yalm_stream_t s);
+                          const float *rel, const int *bucket, const float *hb, const float *table, int ldt, int n, int n_heads, int n_kv, int dk,
+                          int ring, int window, int keep, float scale, int context, int pos0, const int *ctl, yalm_stream_t s);
 /* x[m] += a[m] (+ b[m]) + sum_{j < nsum} y[m * nsum + j]  (a, b, y optional). */
 int yalm_residual_sum_rows(float *x, const float *a, const float *b, const float *y, int ldy, int nsum, int n, int dim, yalm_stream_t s);
 int yalm_softcap_rows(float *z, int n, int dim, float cap, yalm_stream_t s);

@@ -129,7 +129,7 @@ def test_short_convolution_in_portions(taps, sizes):
 # ---- the sigmoid attention alone -------------------------------------------------------------------------------------------
 def run_sigmoid_attention(q, k, rel, hb, gate, window, keep, scale, far, ring, sizes, cache_f32=1, mma=False):
     L = api.lib()
-    L.yalm_attn_sigmoid_mma.argtypes = [vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp]
+    L.yalm_attn_sigmoid_mma.argtypes = [vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp]
     L.yalm_qk_bias_append_rows.argtypes = [vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp]
     L.yalm_attn_sigmoid_rows.argtypes = [vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, vp, vp]
     L.yalm_attn_sigmoid_workspace.restype = C.c_size_t
@@ -145,12 +145,14 @@ def run_sigmoid_attention(q, k, rel, hb, gate, window, keep, scale, far, ring, s
     ws = torch.zeros(L.yalm_attn_sigmoid_workspace(d), device="cuda")
     out = torch.zeros(T, H * d, device="cuda")
     kp = window > 0 and keep or 0
+    # the per-head table form of the same bias; every other call goes without it
+    table = dev((rel[[O.distance_bucket(n, rel.shape[0], far) for n in range(T)]] + hb).T) if mma and window % 2 else None
     for at, n in portions(T, sizes):
         ok(L.yalm_qk_bias_append_rows(ptr(rows[at:]), vp(rows[at:].data_ptr() + 4 * H * d), ld, None, None, ptr(ringb), ptr(firstb), n, H, G, d, ring, kp,
                                       cache_f32, at, None, None), "qk_bias_append_rows")
         if mma:
             ok(L.yalm_attn_sigmoid_mma(ptr(out[at:]), H * d, ptr(rows[at:]), ld, ptr(ringb), ptr(firstb), ptr(gd[at:]) if gd is not None else None, H * d,
-                                       ptr(reld), ptr(bucket), ptr(hbd), n, H, G, d, ring, window, kp, scale, T, at, None, None), "attn_sigmoid_mma")
+                                       ptr(reld), ptr(bucket), ptr(hbd), ptr(table), T, n, H, G, d, ring, window, kp, scale, T, at, None, None), "attn_sigmoid_mma")
             continue
         ok(L.yalm_attn_sigmoid_rows(ptr(out[at:]), H * d, ptr(rows[at:]), ld, ptr(ringb), ptr(firstb), ptr(gd[at:]) if gd is not None else None, H * d, ptr(reld),
                                     ptr(bucket), ptr(hbd), ptr(ws), n, H, G, d, ring, window, kp, scale, cache_f32, T, at, None, None), "attn_sigmoid_rows")

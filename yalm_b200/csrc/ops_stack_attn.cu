@@ -235,8 +235,9 @@ template <int D>
 __global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
                                                                const __nv_bfloat16 *__restrict__ ring_buf, const __nv_bfloat16 *__restrict__ first_buf,
                                                                const float *__restrict__ gate, int ldg, const float *__restrict__ rel,
-                                                               const int *__restrict__ bucket, const float *__restrict__ hb, int n, int n_heads, int n_kv,
-                                                               int ring, int window, int keep, float scale, int tb, int pos0, const int *__restrict__ ctl) {
+                                                               const int *__restrict__ bucket, const float *__restrict__ hb,
+                                                               const float *__restrict__ table, int ldt, int n, int n_heads, int n_kv, int ring, int window,
+                                                               int keep, float scale, int tb, int pos0, const int *__restrict__ ctl) {
 	constexpr int LD = D + 8, KS = D / 16, OT = D / 8;
 	extern __shared__ __align__(16) __nv_bfloat16 smb[];
 	__nv_bfloat16 *Qs = smb, *Kbuf = Qs + 64 * LD;
@@ -258,9 +259,13 @@ __global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(float *__restrict
 	auto lo_of = [&](int i) { return window > 0 ? max(0, i - window + 1) : 0; };
 	const int lo_min = lo_of(i_first);
 	const int nfirst_max = min(keep, lo_of(i_last));
-	for (int d = threadIdx.x; d < tb; d += 128) relt[d] = (rel && d <= i_last) ? rel[(size_t)bucket[d] * n_heads + h] + hbh : hbh;
+	// table (optional): the same bias per (head, distance), rel[bucket[d], h] + hb[h], laid out for one coalesced read
+	const float *trow = table ? table + (size_t)h * ldt : nullptr;
+	for (int d = threadIdx.x; d < tb; d += 128)
+		relt[d] = d > i_last ? hbh : trow ? trow[d] : rel ? rel[(size_t)bucket[d] * n_heads + h] + hbh : hbh;
 	__syncthreads();
-	auto bias_of = [&](int dist) { return dist < tb ? relt[dist] : (rel ? rel[(size_t)bucket[dist] * n_heads + h] + hbh : hbh); };
+	auto bias_far = [&](int dist) { return trow ? trow[dist] : rel ? rel[(size_t)bucket[dist] * n_heads + h] + hbh : hbh; };
+	const bool table_covers = i_last - lo_min < tb; // every distance inside the window of this CTA's rows is in the table
 	uint32_t qf[KS][4];
 	{
 		const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, cofs = (lane >> 4) * 8;
@@ -320,19 +325,38 @@ __global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(float *__restrict
 		}
 		// ---- weights: an interval of positions per row, fp32 sigmoid ----
 		const int minA = first ? 0 : loA, maxA = first ? nfA - 1 : iA, minB = first ? 0 : loB, maxB = first ? nfB - 1 : iB;
+		// One stage at a time over all 32 scores of the lane, in place: every stage is a batch of independent instructions
+		// (an element-by-element chain of table read, exponential and reciprocal leaves one warp per scheduler waiting).
+		const bool from_table = !first && table_covers; // uniform: ring tiles read the shared-memory table without a branch
+#pragma unroll
+		for (int t = 0; t < 8; ++t) {
+			const int key = base + t * 8 + (lane & 3) * 2;
+#pragma unroll
+			for (int e = 0; e < 4; ++e) {
+				const int kk = key + (e & 1), i = e < 2 ? iA : iB;
+				float b;
+				if (from_table) b = relt[min(max(i - kk, 0), tb - 1)];
+				else b = (kk >= (e < 2 ? minA : minB) && kk <= (e < 2 ? maxA : maxB)) ? bias_far(i - kk) : 0.f;
+				s[t][e] = -(s[t][e] * scale + b);
+			}
+		}
+		// fast exponential and reciprocal: the weight is rounded to bf16 as the operand of the second product
+#pragma unroll
+		for (int t = 0; t < 8; ++t)
+#pragma unroll
+			for (int e = 0; e < 4; ++e) s[t][e] = __expf(s[t][e]);
+#pragma unroll
+		for (int t = 0; t < 8; ++t)
+#pragma unroll
+			for (int e = 0; e < 4; ++e) s[t][e] = __fdividef(1.0f, 1.0f + s[t][e]);
 		uint32_t pf[4][4];
 #pragma unroll
 		for (int t = 0; t < 8; ++t) {
 			const int key = base + t * 8 + (lane & 3) * 2;
-			float w[4];
-#pragma unroll
-			for (int e = 0; e < 4; ++e) {
-				const int kk = key + (e & 1), lo = e < 2 ? minA : minB, hi = e < 2 ? maxA : maxB, i = e < 2 ? iA : iB;
-				// fast exponential and reciprocal: the weight is rounded to bf16 as the operand of the second product
-				w[e] = (kk >= lo && kk <= hi) ? __fdividef(1.0f, 1.0f + __expf(-(s[t][e] * scale + bias_of(i - kk)))) : 0.f;
-			}
-			pf[t >> 1][(t & 1) * 2] = pack_bf2(w[0], w[1]);
-			pf[t >> 1][(t & 1) * 2 + 1] = pack_bf2(w[2], w[3]);
+			const float w0 = (key >= minA && key <= maxA) ? s[t][0] : 0.f, w1 = (key + 1 >= minA && key + 1 <= maxA) ? s[t][1] : 0.f;
+			const float w2 = (key >= minB && key <= maxB) ? s[t][2] : 0.f, w3 = (key + 1 >= minB && key + 1 <= maxB) ? s[t][3] : 0.f;
+			pf[t >> 1][(t & 1) * 2] = pack_bf2(w0, w1);
+			pf[t >> 1][(t & 1) * 2 + 1] = pack_bf2(w2, w3);
 		}
 		// ---- O += P K ----
 		{
@@ -348,26 +372,30 @@ __global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(float *__restrict
 				}
 		}
 	}
+	// the output gate (raw values, 8-byte aligned pairs): all reads first, then the sigmoids
+	float2 gA[OT], gB[OT];
 #pragma unroll
 	for (int t = 0; t < OT; ++t) {
 		const int d = h * D + t * 8 + (lane & 3) * 2;
-		if (rA < n) {
-			float2 gv = make_float2(1.f, 1.f);
-			if (gate) gv = make_float2(1.0f / (1.0f + expf(-gate[(size_t)rA * ldg + d])), 1.0f / (1.0f + expf(-gate[(size_t)rA * ldg + d + 1])));
-			*reinterpret_cast<float2 *>(out + (size_t)rA * ldo + d) = make_float2(o[t][0] * gv.x, o[t][1] * gv.y);
+		gA[t] = (gate && rA < n) ? *reinterpret_cast<const float2 *>(gate + (size_t)rA * ldg + d) : make_float2(0.f, 0.f);
+		gB[t] = (gate && rB < n) ? *reinterpret_cast<const float2 *>(gate + (size_t)rB * ldg + d) : make_float2(0.f, 0.f);
+	}
+#pragma unroll
+	for (int t = 0; t < OT; ++t) {
+		const int d = h * D + t * 8 + (lane & 3) * 2;
+		if (gate) {
+			o[t][0] *= __fdividef(1.0f, 1.0f + __expf(-gA[t].x)), o[t][1] *= __fdividef(1.0f, 1.0f + __expf(-gA[t].y));
+			o[t][2] *= __fdividef(1.0f, 1.0f + __expf(-gB[t].x)), o[t][3] *= __fdividef(1.0f, 1.0f + __expf(-gB[t].y));
 		}
-		if (rB < n) {
-			float2 gv = make_float2(1.f, 1.f);
-			if (gate) gv = make_float2(1.0f / (1.0f + expf(-gate[(size_t)rB * ldg + d])), 1.0f / (1.0f + expf(-gate[(size_t)rB * ldg + d + 1])));
-			*reinterpret_cast<float2 *>(out + (size_t)rB * ldo + d) = make_float2(o[t][2] * gv.x, o[t][3] * gv.y);
-		}
+		if (rA < n) *reinterpret_cast<float2 *>(out + (size_t)rA * ldo + d) = make_float2(o[t][0], o[t][1]);
+		if (rB < n) *reinterpret_cast<float2 *>(out + (size_t)rB * ldo + d) = make_float2(o[t][2], o[t][3]);
 	}
 }
 
 template <int D>
 static int launch_sigmoid_mma(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
-                              const float *rel, const int *bucket, const float *hb, int n, int n_heads, int n_kv, int ring, int window, int keep, float scale,
-                              int context, int pos0, const int *ctl, cudaStream_t st) {
+                              const float *rel, const int *bucket, const float *hb, const float *table, int ldt, int n, int n_heads, int n_kv, int ring,
+                              int window, int keep, float scale, int context, int pos0, const int *ctl, cudaStream_t st) {
 	const int tb = std::min(4096, window > 0 ? window + 64 : std::max(64, context));
 	const size_t smem = sizeof(__nv_bfloat16) * (3 * 64 * (D + 8)) + sizeof(float) * tb;
 	static size_t configured = 0;
@@ -376,8 +404,8 @@ static int launch_sigmoid_mma(float *out, int ldo, const float *q, int ldq, cons
 		configured = smem;
 	}
 	attn_sigmoid_mma_kernel<D><<<dim3((n + 63) / 64, n_heads), 128, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)ring_buf,
-	                                                                            (const __nv_bfloat16 *)first_buf, gate, ldg, rel, bucket, hb, n, n_heads, n_kv, ring,
-	                                                                            window, keep, scale, tb, pos0, ctl);
+	                                                                            (const __nv_bfloat16 *)first_buf, gate, ldg, rel, bucket, hb, table, ldt, n, n_heads,
+	                                                                            n_kv, ring, window, keep, scale, tb, pos0, ctl);
 	return (int)cudaGetLastError();
 }
 
@@ -420,15 +448,16 @@ extern "C" int yalm_attn_sigmoid_mma_shape(int dk) {
 }
 
 // The tensor-core route of yalm_attn_sigmoid_rows: bf16 ring and kept-first buffer, head sizes of yalm_attn_sigmoid_mma_shape,
-// q rows 16-byte aligned (ldq a multiple of 4 floats), out and gate rows 8-byte aligned.
+// q rows 16-byte aligned (ldq a multiple of 4 floats), out and gate rows 8-byte aligned.  table (optional, (n_heads, ldt) with
+// ldt >= the most positions a sequence reaches): rel[bucket[d], h] + hb[h] per head and distance, read instead of rel / bucket / hb.
 extern "C" int yalm_attn_sigmoid_mma(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
-                                     const float *rel, const int *bucket, const float *hb, int n, int n_heads, int n_kv, int dk, int ring, int window,
-                                     int keep, float scale, int context, int pos0, const int *ctl, yalm_stream_t s) {
+                                     const float *rel, const int *bucket, const float *hb, const float *table, int ldt, int n, int n_heads, int n_kv,
+                                     int dk, int ring, int window, int keep, float scale, int context, int pos0, const int *ctl, yalm_stream_t s) {
 	if (!out || !q || !ring_buf || n < 1 || n_kv < 1 || n_heads % n_kv || (keep > 0 && !first_buf) || (rel && !bucket) || ldq % 4 || ldo % 2 ||
-	    ((uintptr_t)q & 15) || ((uintptr_t)out & 7) || !yalm_attn_sigmoid_mma_shape(dk))
+	    ((uintptr_t)q & 15) || ((uintptr_t)out & 7) || (gate && (ldg % 2 || ((uintptr_t)gate & 7))) || !yalm_attn_sigmoid_mma_shape(dk))
 		return YALM_EINVAL;
 	cudaStream_t st = (cudaStream_t)s;
-	if (dk == 32) return launch_sigmoid_mma<32>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
-	if (dk == 64) return launch_sigmoid_mma<64>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
-	return launch_sigmoid_mma<128>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
+	if (dk == 32) return launch_sigmoid_mma<32>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, table, ldt, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
+	if (dk == 64) return launch_sigmoid_mma<64>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, table, ldt, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
+	return launch_sigmoid_mma<128>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, table, ldt, n, n_heads, n_kv, ring, window, keep, scale, context, pos0, ctl, st);
 }

@@ -55,6 +55,7 @@ struct StackLayer {
 	float *qkb = nullptr;                    // q bias then k bias
 	float *rel = nullptr, *head_bias = nullptr;
 	int *bucket = nullptr;                   // distance -> row of rel, max_seq_len entries
+	float *bias_table = nullptr;             // (heads, max_seq_len): rel[bucket[d], h] + head_bias[h], what the tensor-core kernel stages
 	void *kfirst = nullptr;                  // (kv heads, keep_first, dim): the kept first tokens' keys
 	// delta rule: columns [q | k | v | beta | decay stage 1 | gate stage 1]
 	int o_dq = 0, o_beta = 0, o_a1 = 0, o_g1 = 0;
@@ -305,6 +306,13 @@ void Model::build_stack(YALMData &data) {
 						b[n] = n < half ? n
 						                : std::min(rows - 1, half + (int)std::floor(std::log((double)n / half) / std::log((double)m.rel_far / half) * (rows - half)));
 					pl.push_back({(void **)&L->bucket, {{b, (size_t)c.max_seq_len * sizeof(int)}}});
+					const float *rel32 = static_cast<const float *>(vec32(tensor(i, TensorRole::RelBias, -1, {m.rel_rows, m.heads})).first);
+					const float *hb32 = static_cast<const float *>(vec32(tensor(i, TensorRole::HeadBias, -1, {m.heads})).first);
+					_host_converted.emplace_back((size_t)m.heads * c.max_seq_len * sizeof(float));
+					float *tb = reinterpret_cast<float *>(_host_converted.back().data());
+					for (int hh = 0; hh < m.heads; ++hh)
+						for (int n = 0; n < c.max_seq_len; ++n) tb[(size_t)hh * c.max_seq_len + n] = rel32[(size_t)b[n] * m.heads + hh] + hb32[hh];
+					pl.push_back({(void **)&L->bias_table, {{tb, (size_t)m.heads * c.max_seq_len * sizeof(float)}}});
 				}
 				pl.push_back({(void **)&L->conv_w, {vec32(tensor(i, TensorRole::DeltaQConv, -1, {dk, d.conv})), vec32(tensor(i, TensorRole::DeltaKConv, -1, {dk, d.conv})),
 				                                    vec32(tensor(i, TensorRole::DeltaVConv, -1, {dv, d.conv}))}});
@@ -616,8 +624,8 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 		                                ctl, st));
 		// many rows over the bf16 ring: tensor cores; decode-sized calls, the fp32 ring and other head sizes: the SIMT kernel
 		if (!f32 && n >= 16 && ldp % 4 == 0 && L.o_q % 4 == 0 && L.o_gate % 2 == 0 && no % 2 == 0 && yalm_attn_sigmoid_mma_shape(m.dim) && !attn_mma_off())
-			ST_TRY(yalm_attn_sigmoid_mma(S.att, no, P + L.o_q, ldp, L.kring, L.kfirst, P + L.o_gate, ldp, L.rel, L.bucket, L.head_bias, n, m.heads, m.kv_heads,
-			                             m.dim, L.ring, m.window, keep, m.scale, c.max_seq_len, pos0, ctl, st));
+			ST_TRY(yalm_attn_sigmoid_mma(S.att, no, P + L.o_q, ldp, L.kring, L.kfirst, P + L.o_gate, ldp, L.rel, L.bucket, L.head_bias, L.bias_table, c.max_seq_len, n, m.heads,
+			                             m.kv_heads, m.dim, L.ring, m.window, keep, m.scale, c.max_seq_len, pos0, ctl, st));
 		else
 			ST_TRY(yalm_attn_sigmoid_rows(S.att, no, P + L.o_q, ldp, L.kring, L.kfirst, P + L.o_gate, ldp, L.rel, L.bucket, L.head_bias, S.attn_ws, n, m.heads,
 			                              m.kv_heads, m.dim, L.ring, m.window, keep, m.scale, f32, c.max_seq_len, pos0, ctl, st));
