@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(256) delta_prep_rows_kernel(float *__restrict_
 }
 
 // out[m, c] = rms_part(y[m, c] * silu(z[m, c])) * w[c], the row cut into gridDim.y equal parts.  grid (rows, parts).
-__global__ void __launch_bounds__(256) gated_group_norm_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ y, int ldy,
+__global__ void __launch_bounds__(1024) gated_group_norm_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ y, int ldy,
                                                                     const float *__restrict__ z, int ldz, const float *__restrict__ w, int part, float eps) {
 	__shared__ float red[33];
 	const int m = blockIdx.x, c0 = blockIdx.y * part;
@@ -520,7 +520,9 @@ extern "C" int yalm_delta_prep_rows(float *q, float *k, int ldqk, float *beta, i
 extern "C" int yalm_gated_group_norm_rows(float *out, int ldo, const float *y, int ldy, const float *z, int ldz, const float *w, int n, int dim, int parts,
                                           float eps, yalm_stream_t s) {
 	if (!out || !y || !z || !w || n < 1 || parts < 1 || dim < parts || dim % parts) return YALM_EINVAL;
-	gated_group_norm_rows_kernel<<<dim3(n, parts), 256, 0, (cudaStream_t)s>>>(out, ldo, y, ldy, z, ldz, w, dim / parts, eps);
+	// few rows (decoding): the part's channels spread over more threads
+	const int threads = n * parts < 64 ? std::min(1024, std::max(256, (dim / parts + 127) / 128 * 32)) : 256;
+	gated_group_norm_rows_kernel<<<dim3(n, parts), threads, 0, (cudaStream_t)s>>>(out, ldo, y, ldy, z, ldz, w, dim / parts, eps);
 	return (int)cudaGetLastError();
 }
 
