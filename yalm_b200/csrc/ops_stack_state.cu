@@ -105,13 +105,14 @@ __global__ void __launch_bounds__(128) conv_state_rows_kernel(const float *__res
 //   S <- decay * S   (decay: one number per head, or one per head and key channel, acting on rows)
 //   u = beta * (v - S^T k)   (delta rule)   or   u = vscale * v
 //   S <- S + k u^T;   o = S^T q  (+ skip * v)
-// One CTA owns 16 columns of one head; 8 neighbouring lanes share a column, lane `sub` holding the rows e * 8 + sub in
-// registers, so the two dot products of a step are EPL multiply-adds (four partial sums) and three shuffles.  k, q, the
-// decays and v of 8 positions at a time go global -> shared with cp.async into one of two stages: the next 8 load while
-// these are consumed.  The reduction of a position's output is carried into the next position's step, where it shares the
-// shuffle rounds of that step's S^T k, so only the recurrence itself (decay, S^T k, update) is a serial chain.  The order of
-// every sum is fixed, so a position's output does not depend on how the rows were cut into calls.  State in global memory:
-// (head, column, row) fp32.
+// One CTA owns 16 columns of one head; 8 neighbouring lanes share a column, lane `sub` holding the EPL consecutive rows
+// sub * EPL .. in registers, so the two dot products of a step are EPL multiply-adds (four partial sums) and three shuffles.
+// k, q, the decays and v of 8 positions at a time go global -> shared with cp.async into one of two stages: the next 8 load
+// while these are consumed.  In shared memory a position's row is cut into the 8 lanes' segments, padded so that the lanes'
+// 16-byte reads fall into different banks.  The reduction of a position's output is carried into the next position's step,
+// where it shares the shuffle rounds of that step's S^T k, so only the recurrence itself (decay, S^T k, update) is a serial
+// chain.  The order of every sum is fixed, so a position's output does not depend on how the rows were cut into calls.
+// State in global memory: (head, column, row) fp32.
 struct ScanArgs {
 	float *out;
 	int ldo;
@@ -133,20 +134,43 @@ __device__ __forceinline__ void cp_async16f(float *smem, const float *gmem) {
 }
 
 template <int EPL>
+struct ScanLayout {
+	static constexpr int SEG = EPL + (EPL >= 8 ? 4 : 0); // floats between two lanes' segments of a row
+	static constexpr int DP = 8 * SEG;
+	static constexpr int STAGE = 3 * kScanTok * DP + kScanTok * kScanCols + kScanTok * 4; // k, q, decay rows; v; (decay, vscale, beta) per position
+};
+
+// EPL consecutive floats of a shared-memory segment into registers, with the widest aligned reads
+template <int EPL>
+__device__ __forceinline__ void load_seg(float (&r)[EPL], const float *p) {
+	if constexpr (EPL % 4 == 0) {
+#pragma unroll
+		for (int e = 0; e < EPL; e += 4) {
+			const float4 v = *reinterpret_cast<const float4 *>(p + e);
+			r[e] = v.x, r[e + 1] = v.y, r[e + 2] = v.z, r[e + 3] = v.w;
+		}
+	} else if constexpr (EPL == 2) {
+		const float2 v = *reinterpret_cast<const float2 *>(p);
+		r[0] = v.x, r[1] = v.y;
+	} else
+		r[0] = p[0];
+}
+
+template <int EPL>
 __global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
-	constexpr int DP = EPL * 8, TOK = kScanTok;
-	constexpr int STAGE = 3 * TOK * DP + TOK * kScanCols + TOK * 4; // k, q, decay rows; v; (decay, vscale, beta) per position
+	using LO = ScanLayout<EPL>;
+	constexpr int SEG = LO::SEG, DP = LO::DP, TOK = kScanTok, STAGE = LO::STAGE;
 	extern __shared__ __align__(16) float scan_sm[];
 	const int h = blockIdx.y, kh = h / a.rep, c0 = blockIdx.x * kScanCols;
 	const int tid = threadIdx.x, col = tid >> 3, sub = tid & 7;
 	const bool live = c0 + col < a.P;
 	const bool fresh = first_pos(a.ctl, a.pos0) == 0;
-	float *sp = a.state + ((size_t)h * a.P + min(c0 + col, a.P - 1)) * a.D;
+	float *sp = a.state + ((size_t)h * a.P + min(c0 + col, a.P - 1)) * a.D + sub * EPL;
 	float s[EPL];
 #pragma unroll
-	for (int e = 0; e < EPL; ++e) s[e] = (!fresh && e * 8 + sub < a.D) ? sp[e * 8 + sub] : 0.f;
+	for (int e = 0; e < EPL; ++e) s[e] = (!fresh && sub * EPL + e < a.D) ? sp[e] : 0.f;
 	const float skip = a.skip ? a.skip[h] : 0.f;
-	// what the copies never write: rows past D, columns past P, and the defaults of absent per-position scalars
+	// what the copies never write: rows past D, the padding, columns past P, and the defaults of absent per-position scalars
 	for (int idx = tid; idx < 2 * STAGE; idx += blockDim.x) {
 		const int r = idx % STAGE;
 		scan_sm[idx] = (r >= 3 * TOK * DP + TOK * kScanCols && (r - 3 * TOK * DP - TOK * kScanCols) % 4 < 2) ? 1.f : 0.f;
@@ -155,20 +179,20 @@ __global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
 	auto issue = [&](int t0, int stage) {
 		float *ks = scan_sm + stage * STAGE, *qs = ks + TOK * DP, *gs = qs + TOK * DP, *vs = gs + TOK * DP, *sc = vs + TOK * kScanCols;
 		const int tc = min(TOK, a.n - t0);
-		if (a.vec) {
+		if (a.vec && EPL >= 4) {
 			const int D4 = a.D >> 2;
 			for (int idx = tid; idx < tc * D4; idx += blockDim.x) {
-				const int t = idx / D4, i = (idx % D4) * 4;
-				cp_async16f(ks + t * DP + i, a.k + (size_t)(t0 + t) * a.ldk + kh * a.D + i);
-				cp_async16f(qs + t * DP + i, a.q + (size_t)(t0 + t) * a.ldq + kh * a.D + i);
-				if (a.decay_per_channel) cp_async16f(gs + t * DP + i, a.decay + (size_t)(t0 + t) * a.ldd + h * a.D + i);
+				const int t = idx / D4, i = (idx % D4) * 4, at = t * DP + (i / EPL) * SEG + i % EPL;
+				cp_async16f(ks + at, a.k + (size_t)(t0 + t) * a.ldk + kh * a.D + i);
+				cp_async16f(qs + at, a.q + (size_t)(t0 + t) * a.ldq + kh * a.D + i);
+				if (a.decay_per_channel) cp_async16f(gs + at, a.decay + (size_t)(t0 + t) * a.ldd + h * a.D + i);
 			}
 		} else {
 			for (int idx = tid; idx < tc * a.D; idx += blockDim.x) {
-				const int t = idx / a.D, i = idx % a.D;
-				cp_async4(ks + t * DP + i, a.k + (size_t)(t0 + t) * a.ldk + kh * a.D + i);
-				cp_async4(qs + t * DP + i, a.q + (size_t)(t0 + t) * a.ldq + kh * a.D + i);
-				if (a.decay_per_channel) cp_async4(gs + t * DP + i, a.decay + (size_t)(t0 + t) * a.ldd + h * a.D + i);
+				const int t = idx / a.D, i = idx % a.D, at = t * DP + (i / EPL) * SEG + i % EPL;
+				cp_async4(ks + at, a.k + (size_t)(t0 + t) * a.ldk + kh * a.D + i);
+				cp_async4(qs + at, a.q + (size_t)(t0 + t) * a.ldq + kh * a.D + i);
+				if (a.decay_per_channel) cp_async4(gs + at, a.decay + (size_t)(t0 + t) * a.ldd + h * a.D + i);
 			}
 		}
 		for (int idx = tid; idx < tc * kScanCols; idx += blockDim.x) {
@@ -195,11 +219,15 @@ __global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
 		__syncthreads();
 		const float *ks = scan_sm + (c & 1) * STAGE, *qs = ks + TOK * DP, *gs = qs + TOK * DP, *vs = gs + TOK * DP, *sc = vs + TOK * kScanCols;
 		for (int t = 0; t < tc; ++t) {
-			const float *kt = ks + t * DP + sub, *qt = qs + t * DP + sub, *gt = gs + t * DP + sub;
+			float kt[EPL], qt[EPL];
+			load_seg<EPL>(kt, ks + t * DP + sub * SEG);
+			load_seg<EPL>(qt, qs + t * DP + sub * SEG);
 			const float vv = vs[t * kScanCols + col];
 			if (a.decay_per_channel) {
+				float gt[EPL];
+				load_seg<EPL>(gt, gs + t * DP + sub * SEG);
 #pragma unroll
-				for (int e = 0; e < EPL; ++e) s[e] *= gt[e * 8];
+				for (int e = 0; e < EPL; ++e) s[e] *= gt[e];
 			} else {
 				const float d = sc[t * 4];
 #pragma unroll
@@ -209,7 +237,7 @@ __global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
 			if (a.beta) {
 				float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-				for (int e = 0; e < EPL; ++e) d4[e & 3] = fmaf(s[e], kt[e * 8], d4[e & 3]);
+				for (int e = 0; e < EPL; ++e) d4[e & 3] = fmaf(s[e], kt[e], d4[e & 3]);
 				float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
 				dot += __shfl_xor_sync(kFull, dot, 4), po += __shfl_xor_sync(kFull, po, 4);
 				dot += __shfl_xor_sync(kFull, dot, 2), po += __shfl_xor_sync(kFull, po, 2);
@@ -223,8 +251,8 @@ __global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
 			float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
 			for (int e = 0; e < EPL; ++e) {
-				s[e] = fmaf(kt[e * 8], u, s[e]);
-				o4[e & 3] = fmaf(s[e], qt[e * 8], o4[e & 3]);
+				s[e] = fmaf(kt[e], u, s[e]);
+				o4[e & 3] = fmaf(s[e], qt[e], o4[e & 3]);
 			}
 			po = (o4[0] + o4[1]) + (o4[2] + o4[3]), pvv = vv;
 			pout = a.out + (size_t)(t0 + t) * a.ldo + h * a.P + min(c0 + col, a.P - 1);
@@ -236,7 +264,7 @@ __global__ void __launch_bounds__(kScanCols * 8) state_scan_kernel(ScanArgs a) {
 	if (live) {
 #pragma unroll
 		for (int e = 0; e < EPL; ++e)
-			if (e * 8 + sub < a.D) sp[e * 8 + sub] = s[e];
+			if (sub * EPL + e < a.D) sp[e] = s[e];
 	}
 }
 
@@ -486,7 +514,7 @@ extern "C" int yalm_state_scan_rows(float *out, int ldo, const float *k, int ldk
 	cudaStream_t st = (cudaStream_t)s;
 #define SCAN_CASE(EPL_)                                                                                                                      \
 	{                                                                                                                                        \
-		constexpr size_t smem = sizeof(float) * 2 * (3 * kScanTok * EPL_ * 8 + kScanTok * kScanCols + kScanTok * 4);                        \
+		constexpr size_t smem = sizeof(float) * 2 * ScanLayout<EPL_>::STAGE;                                                                 \
 		static bool configured = false;                                                                                                      \
 		if (smem > 48 * 1024 && !configured) {                                                                                               \
 			YALM_TRY(cudaFuncSetAttribute(state_scan_kernel<EPL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
