@@ -207,18 +207,22 @@ def test_sigmoid_attention_far_keys_among_hundreds():
     assert np.abs(want[660, 0] - without[660, 0] - k3).max() < 1e-3       # the kept token's share is one whole key vector
     # the whole context without a window: the far key is one among 700
     want = O.sigmoid_attention_core(q, k, rel, hb, 0, 0, 1.0, far=100)
-    got = run_sigmoid_attention(q, k, rel, hb, None, 0, 0, 1.0, 100, T, [640, 1, 1, 58])
+    got = run_sigmoid_attention(q, k, rel, hb, None, 0, 0, 1.0, 100, T, [630, 1, 1, 68])
     close_enough(got, want, 1e-5)
 
 
-def test_sigmoid_attention_over_a_bf16_ring():
-    T, H, G, d = 60, 4, 2, 16
+@pytest.mark.parametrize("d,H,G,sizes", [(16, 4, 2, [5, 1, 9]), (8, 4, 2, [1]), (64, 8, 2, [1, 3]), (256, 2, 2, [13, 1]), (16, 8, 1, [12]), (32, 16, 2, [13]), (24, 4, 2, [4])])
+def test_sigmoid_attention_over_a_bf16_ring(d, H, G, sizes):
+    """Decode-sized calls over the serving cache: rows read as 16-byte pieces by lane groups (head sizes 8 * 2^k; 24: lane per key)."""
+    T = 60
     q, k = crafted(T, H, G, d, 11, 2, seed=4)
-    rel, hb = np.zeros((8, H)), np.full(H, -20.0)
+    rng = np.random.default_rng(d)
+    rel, hb, gate = rng.standard_normal((8, H)), np.full(H, -20.0), rng.standard_normal((T, H, d))
     kr = O.from_bf16_bits(O.to_bf16_bits(k.astype(np.float32))).reshape(k.shape).astype(np.float64)
-    want = O.sigmoid_attention_core(q, kr, rel, hb, 11, 2, 1.0, far=20)
-    got = run_sigmoid_attention(q, k, rel, hb, None, 11, 2, 1.0, 20, 24, [5, 1, 9], cache_f32=0)
-    close_enough(got, want, 2e-2)
+    want = O.sigmoid_attention_core(q, kr, rel, hb, 11, 2, 1.0, far=20) * O.sigmoid(gate)
+    got = run_sigmoid_attention(q, k, rel, hb, gate, 11, 2, 1.0, 20, 24, sizes, cache_f32=0)
+    close_enough(got, want, 1e-5)
+    assert np.abs(O.sigmoid_attention_core(q, kr, rel, hb, 12, 2, 1.0, far=20) * O.sigmoid(gate) - want).max() > 0.3
 
 
 @pytest.mark.parametrize("d,window,keep,sizes,ring", [(32, 9, 3, [1000], 240), (64, 70, 5, [64, 17, 100], 170), (128, 33, 40, [16, 130], 163), (64, 0, 0, [90, 16], 230),

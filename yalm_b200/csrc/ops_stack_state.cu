@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "launch.h"
 #include "stack_rows.cuh"
@@ -448,6 +449,134 @@ __global__ void __launch_bounds__(kSigWarps * 32) attn_sigmoid_rows_kernel(float
 		else out[(size_t)m * ldo + (size_t)h * dk + c] = gate ? o * sigmoidf_(gate[(size_t)m * ldg + (size_t)h * dk + c]) : o;
 	}
 }
+// The same attention for a bf16 ring whose head size is 8, 16, ..., 256: every key row is read as 16-byte pieces by dk / 8
+// neighbouring lanes, so that one warp instruction fetches whole rows and eight of them are in flight per lane; each lane
+// keeps its 8 channels of the R queries and of the R sums in registers.  The scores of a 32-key tile pass through shared
+// memory to the lane = key layout, where the bias is added and the sigmoid taken, and back for the weighted sum, which
+// reads the same rows again (the values are the keys).  Same grid, splits, partials and merge as attn_sigmoid_rows_kernel.
+template <int R>
+__global__ void __launch_bounds__(kSigWarps * 32) attn_sigmoid_lanes_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                                            const __nv_bfloat16 *__restrict__ ring_buf,
+                                                                            const __nv_bfloat16 *__restrict__ first_buf, const float *__restrict__ gate,
+                                                                            int ldg, const float *__restrict__ rel, const int *__restrict__ bucket,
+                                                                            const float *__restrict__ hb, float *__restrict__ part, int n_heads, int n_kv,
+                                                                            int dk, int ring, int window, int keep, float scale, int pos0,
+                                                                            const int *__restrict__ ctl) {
+	extern __shared__ __align__(16) float sm[];
+	float *qs = sm;                              // R x dk
+	float *macc = qs + R * dk;                   // kSigWarps x R x dk
+	float *sc = macc + kSigWarps * R * dk;       // kSigWarps x R x 32
+	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
+	const int g = blockIdx.x / hg, h0 = g * rep + (blockIdx.x % hg) * R, nh = min(R, g * rep + rep - h0);
+	const int m = blockIdx.y, z = blockIdx.z, nsplit = gridDim.z;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int i = first_pos(ctl, pos0) + m;
+	const int lo = window > 0 ? max(0, i - window + 1) : 0;
+	const int nfirst = min(keep, lo), ntok = i - lo + 1;
+	for (int e = threadIdx.x; e < R * dk; e += blockDim.x) {
+		const int r = e / dk, d = e % dk;
+		qs[e] = r < nh ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
+	}
+	__syncthreads();
+	const int LK = dk >> 3, sub = lane % LK, rg = lane / LK, rp = 32 / LK; // piece of the row, row within a step, rows per step
+	float qr[R][8], acc[R][8], bias_h[R];
+#pragma unroll
+	for (int r = 0; r < R; ++r) {
+		bias_h[r] = (hb && r < nh) ? hb[h0 + r] : 0.f;
+#pragma unroll
+		for (int j = 0; j < 8; ++j) qr[r][j] = qs[r * dk + sub * 8 + j], acc[r][j] = 0.f;
+	}
+	const __nv_bfloat16 *rbase = ring_buf + (size_t)g * ring * dk + sub * 8, *fbase = first_buf ? first_buf + (size_t)g * keep * dk + sub * 8 : nullptr;
+	float *scw = sc + warp * R * 32;
+	const int ftiles = (nfirst + 31) / 32, ntiles = ftiles + (ntok + 31) / 32, per = (ntiles + nsplit - 1) / nsplit;
+	const int t_end = min(ntiles, (z + 1) * per);
+	constexpr int KU = 8; // row steps in flight
+	for (int t = z * per + warp; t < t_end; t += kSigWarps) {
+		const bool first = t < ftiles;
+		const int idx0 = first ? t * 32 : (t - ftiles) * 32, cnt = min(32, (first ? nfirst : ntok) - idx0);
+		const int j0 = first ? idx0 : lo + idx0; // position of the tile's first key
+		auto row_ptr = [&](int row) { // a row past the end repeats the last one; its weight is zero
+			const int j = j0 + min(row, cnt - 1);
+			return first ? fbase + (size_t)j * dk : rbase + (size_t)(j % ring) * dk;
+		};
+		// ---- scores ----
+		for (int u0 = 0; u0 * rp < cnt; u0 += KU) {
+			uint4 w[KU];
+#pragma unroll
+			for (int u = 0; u < KU; ++u) w[u] = __ldg(reinterpret_cast<const uint4 *>(row_ptr((u0 + u) * rp + rg)));
+#pragma unroll
+			for (int u = 0; u < KU; ++u) {
+				float kf[8], d[R];
+				Elem<YALM_BF16>::unpack(w[u], kf);
+				const int row = (u0 + u) * rp + rg;
+#pragma unroll
+				for (int r = 0; r < R; ++r) {
+					d[r] = 0.f;
+#pragma unroll
+					for (int j = 0; j < 8; ++j) d[r] = fmaf(kf[j], qr[r][j], d[r]);
+				}
+				for (int o = LK >> 1; o > 0; o >>= 1)
+#pragma unroll
+					for (int r = 0; r < R; ++r) d[r] += __shfl_xor_sync(kFull, d[r], o);
+				if (sub == 0 && row < 32) {
+#pragma unroll
+					for (int r = 0; r < R; ++r) scw[r * 32 + row] = d[r];
+				}
+			}
+		}
+		__syncwarp();
+		// ---- weights, lane = key ----
+		{
+			const int b = (bucket && lane < cnt) ? bucket[i - (j0 + lane)] : 0;
+#pragma unroll
+			for (int r = 0; r < R; ++r) {
+				float pv = 0.f;
+				if (lane < cnt && r < nh) pv = sigmoidf_(scw[r * 32 + lane] + (rel ? rel[(size_t)b * n_heads + h0 + r] : 0.f) + bias_h[r]);
+				scw[r * 32 + lane] = pv;
+			}
+		}
+		__syncwarp();
+		// ---- weighted sum of the same rows ----
+		for (int u0 = 0; u0 * rp < cnt; u0 += KU) {
+			uint4 w[KU];
+#pragma unroll
+			for (int u = 0; u < KU; ++u) w[u] = __ldg(reinterpret_cast<const uint4 *>(row_ptr((u0 + u) * rp + rg)));
+#pragma unroll
+			for (int u = 0; u < KU; ++u) {
+				float vf[8];
+				Elem<YALM_BF16>::unpack(w[u], vf);
+				const int row = (u0 + u) * rp + rg;
+#pragma unroll
+				for (int r = 0; r < R; ++r) {
+					const float pk = row < cnt ? scw[r * 32 + row] : 0.f;
+#pragma unroll
+					for (int j = 0; j < 8; ++j) acc[r][j] = fmaf(pk, vf[j], acc[r][j]);
+				}
+			}
+		}
+		__syncwarp(); // the next tile's scores overwrite scw
+	}
+	// the row groups of a warp hold partial sums of the same channels
+	for (int o = 16; o >= LK; o >>= 1)
+#pragma unroll
+		for (int r = 0; r < R; ++r)
+#pragma unroll
+			for (int j = 0; j < 8; ++j) acc[r][j] += __shfl_xor_sync(kFull, acc[r][j], o);
+	if (rg == 0) {
+#pragma unroll
+		for (int r = 0; r < R; ++r)
+#pragma unroll
+			for (int j = 0; j < 8; ++j) macc[(warp * R + r) * dk + sub * 8 + j] = acc[r][j];
+	}
+	__syncthreads();
+	for (int e = threadIdx.x; e < nh * dk; e += blockDim.x) {
+		const int r = e / dk, c = e % dk, h = h0 + r;
+		float o = 0.f;
+		for (int w = 0; w < kSigWarps; ++w) o += macc[(w * R + r) * dk + c];
+		if (part) part[((size_t)(m * n_heads + h) * nsplit + z) * dk + c] = o;
+		else out[(size_t)m * ldo + (size_t)h * dk + c] = gate ? o * sigmoidf_(gate[(size_t)m * ldg + (size_t)h * dk + c]) : o;
+	}
+}
 __global__ void attn_sigmoid_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, const float *__restrict__ gate, int ldg,
                                           int n_heads, int dk, int nsplit) {
 	const int h = blockIdx.x, m = blockIdx.y;
@@ -593,6 +722,20 @@ static int launch_attn_sigmoid(float *out, int ldo, const float *q, int ldq, con
 	return (int)cudaGetLastError();
 }
 
+template <int R>
+static int launch_attn_sigmoid_lanes(float *out, int ldo, const float *q, int ldq, const void *ring_buf, const void *first_buf, const float *gate, int ldg,
+                                     const float *rel, const int *bucket, const float *hb, float *ws, int n, int n_heads, int n_kv, int dk, int ring,
+                                     int window, int keep, float scale, int nsplit, int pos0, const int *ctl, cudaStream_t st) {
+	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
+	const size_t smem = sizeof(float) * ((size_t)R * dk + (size_t)kSigWarps * R * dk + kSigWarps * R * 32);
+	if (smem > 48 * 1024) return YALM_EINVAL;
+	attn_sigmoid_lanes_kernel<R><<<dim3(n_kv * hg, n, nsplit), kSigWarps * 32, smem, st>>>(
+	    out, ldo, q, ldq, (const __nv_bfloat16 *)ring_buf, (const __nv_bfloat16 *)first_buf, gate, ldg, rel, bucket, hb, nsplit > 1 ? ws : nullptr, n_heads, n_kv,
+	    dk, ring, window, keep, scale, pos0, ctl);
+	if (nsplit > 1) attn_sigmoid_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, gate, ldg, n_heads, dk, nsplit);
+	return (int)cudaGetLastError();
+}
+
 // rel: (rows, n_heads) fp32 with bucket[distance] naming the row, or null; hb: (n_heads) or null; gate: (n, n_heads * dk)
 // raw gate values with row stride ldg, or null.  workspace: yalm_attn_sigmoid_workspace(dk) floats or null (never split);
 // context: the most positions a sequence reaches.
@@ -608,6 +751,20 @@ extern "C" int yalm_attn_sigmoid_rows(float *out, int ldo, const float *q, int l
 		const int most_keys = window > 0 ? window + keep : (context > 0 ? context : ring);
 		const int tiles = (most_keys + 31) / 32 + 1;
 		nsplit = std::min({(296 + ctas - 1) / ctas, std::max(1, (tiles + kSigWarps - 1) / kSigWarps), std::max(1, kSigMaxParts / (n * n_heads)), 64});
+	}
+	// bf16 ring, head sizes 8 * 2^k: rows read as 16-byte pieces by lane groups.  Heads per CTA: four share every key read; with
+	// few CTAs (decoding) fewer heads per CTA spread the same work over more SMs.  YALM_STACK_ATTN_LANES=0: the lane-per-key kernel.
+	static const bool lanes_off = [] { const char *e = getenv("YALM_STACK_ATTN_LANES"); return e && e[0] == '0'; }();
+	if (!cache_f32 && dk >= 8 && (dk & (dk - 1)) == 0 && aligned16(ring_buf) && aligned16(first_buf) && !lanes_off) {
+		int RL = R;
+		while (RL > 1 && (long)n_kv * ((rep + RL - 1) / RL) * n * nsplit < device_info().sms) RL >>= 1;
+#define SIG_LANES(R_)                                                                                                                             \
+	return launch_attn_sigmoid_lanes<R_>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, workspace, n, n_heads, n_kv, dk, ring, window, \
+	                                     keep, scale, nsplit, pos0, ctl, st)
+		if (RL == 1) SIG_LANES(1);
+		if (RL == 2) SIG_LANES(2);
+		SIG_LANES(4);
+#undef SIG_LANES
 	}
 #define SIG_CASE(CT, R_, DVC_)                                                                                                                     \
 	return launch_attn_sigmoid<CT, R_, DVC_>(out, ldo, q, ldq, ring_buf, first_buf, gate, ldg, rel, bucket, hb, workspace, n, n_heads, n_kv, dk, ring, \
