@@ -359,6 +359,26 @@ def test_decode_rows_with_the_block_fusions(tmp_path, monkeypatch):
         close_enough(first, want[:5], tol)
 
 
+def test_decode_rows_on_side_streams_equal_the_serial_order(tmp_path, monkeypatch):
+    """A decode row's experts and second mixer run on side streams (parallel branches of the captured step); the arithmetic is
+    the same, so logits and greedy tokens are identical to the one-stream order."""
+    cfg = four_layers()
+    folder, W = checkpoint(tmp_path, cfg, seed=13)
+    toks = tokens_for(cfg, 60)
+    runs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("YALM_STACK_BRANCHES", flag)
+        m, s = open_model(folder)
+        s.forward_rows(toks[:7], 0, [])
+        one = np.concatenate([s.forward_rows(toks[i:i + 1], i, [0]) for i in range(7, 60)])
+        gen = s.generate_greedy(toks[0], 60, 12)
+        close(m, s)
+        runs.append((one, gen))
+    np.testing.assert_array_equal(runs[0][0], runs[1][0])
+    assert runs[0][1] == runs[1][1]
+    close_enough(runs[0][0], O.forward(cfg, W, toks)[7:])
+
+
 def test_state_given_back_and_used_again(tmp_path):
     cfg = four_layers()
     folder, W = checkpoint(tmp_path, cfg, seed=8)

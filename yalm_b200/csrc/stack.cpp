@@ -219,7 +219,18 @@ struct Model::StackScratch {
 	int *order = nullptr;                       // slot at every place of that order
 	unsigned *ticket = nullptr; // arrival counter of the one-row products with a fused tail (zero between launches)
 	std::vector<Placement> placements; // filled by build_stack, consumed by cuda_stack
-	~StackScratch() { cudaFree(arena); }
+	// decode rows of a parallel block: its independent sublayers (experts, the second mixer) run on side streams that fork from and
+	// join the caller's stream through these events; inside a captured step they become parallel branches of the graph
+	cudaStream_t side[2] = {nullptr, nullptr};
+	cudaEvent_t fork[2] = {nullptr, nullptr}, join[2] = {nullptr, nullptr};
+	~StackScratch() {
+		for (int i = 0; i < 2; ++i) {
+			if (side[i]) cudaStreamDestroy(side[i]);
+			if (fork[i]) cudaEventDestroy(fork[i]);
+			if (join[i]) cudaEventDestroy(join[i]);
+		}
+		cudaFree(arena);
+	}
 };
 
 void Model::build_stack(YALMData &data) {
@@ -478,6 +489,12 @@ void Model::cuda_stack(int device) {
 	cudaMemset(S.arena, 0, total);
 	char *p = S.arena;
 	for (auto &sl : slots) *sl.p = sl.bytes ? p : nullptr, p += pad(sl.bytes);
+	if (s.parallel_block)
+		for (int i = 0; i < 2; ++i)
+			if (cudaStreamCreateWithFlags(&S.side[i], cudaStreamNonBlocking) != cudaSuccess ||
+			    cudaEventCreateWithFlags(&S.fork[i], cudaEventDisableTiming) != cudaSuccess ||
+			    cudaEventCreateWithFlags(&S.join[i], cudaEventDisableTiming) != cudaSuccess)
+				die("stream / event creation failed");
 	if (cudaDeviceSynchronize() != cudaSuccess) die("device error after upload");
 }
 
@@ -514,6 +531,12 @@ static bool gemv_fusable(const Config &c, int n, int K, const void *w, const voi
 static bool block_fuse_on() {
 	const char *e = getenv("YALM_STACK_FUSE_BLOCK");
 	return e && e[0] == '1';
+}
+
+// YALM_STACK_BRANCHES=0: a parallel block's decode row runs its sublayers one after the other on the caller's stream
+static bool branches_off() { // read per call (a captured step keeps the shape it was captured with): tests compare both
+	const char *e = getenv("YALM_STACK_BRANCHES");
+	return e && e[0] == '0';
 }
 
 static bool attn_mma_off() { // YALM_STACK_ATTN_MMA=0: A/B against the SIMT kernel
@@ -588,22 +611,43 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 		ST_TRY(yalm_norm_shift_rows(S.xn, sp.token_shift ? S.hs : nullptr, S.x, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, n, W, pos0, ctl, st));
 		ST_TRY(stack_linear(*this, c, S.a16, P, ldp, sp.token_shift ? S.hs : S.xn, W, L.wproj, n, ldp, W, 1.f, st));
 	}
-	// ---- experts on h (before the mixer, whose last product then carries the block's residual add on decode rows) ----
+	// A decode row is a chain of small launches, each waiting for the one before.  The experts (which read h), the attention and
+	// the delta rule (which read disjoint columns of the projection and own their scratch) are independent: they run on side
+	// streams forked here and joined before the residual add.  One-row products do not touch the shared 16-bit operand buffer.
+	const bool branch = n == 1 && !fuse && !branches_off();
+	cudaStream_t se = st, sr = st; // the experts' and the delta rule's streams
+	// ---- experts on h (before the mixer, whose last product can carry the block's residual add on decode rows) ----
 	const FfnSpec &f = ls.ffn;
 	int nsum = 0;
 	if (f.kind == FfnSpec::Moe) {
+		if (branch) {
+			se = S.side[0];
+			ST_TRY(cudaEventRecord(S.fork[0], st));
+			ST_TRY(cudaStreamWaitEvent(se, S.fork[0], 0));
+		}
 		const int act = f.act == yalm::GluAct::SigmoidScaled ? 2 : f.act == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
 		ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.xn, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
-		                             f.renormalize ? 1 : 0, f.renorm_eps, f.groups, f.keep_groups, st));
+		                             f.renormalize ? 1 : 0, f.renorm_eps, f.groups, f.keep_groups, se));
 		if (S.moe_gu && !ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
-			ST_TRY(stack_moe_grouped(S, L, S.xn, n, act, st));
+			ST_TRY(stack_moe_grouped(S, L, S.xn, n, act, se));
 		else {
 			ST_TRY(yalm_moe_glu_slots(S.h, S.xn, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
-			                          f.weight_on_input ? 1 : 0, st));
-			ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, st));
+			                          f.weight_on_input ? 1 : 0, se));
+			ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, se));
 		}
 		nsum = f.top;
 	}
+	auto join = [&]() -> int { // the side streams' work precedes what follows on the caller's stream
+		if (se != st) {
+			ST_TRY(cudaEventRecord(S.join[0], se));
+			ST_TRY(cudaStreamWaitEvent(st, S.join[0], 0));
+		}
+		if (sr != st) {
+			ST_TRY(cudaEventRecord(S.join[1], sr));
+			ST_TRY(cudaStreamWaitEvent(st, S.join[1], 0));
+		}
+		return 0;
+	};
 	const float *mix_b = nullptr;
 	if (ls.kind == yalm::MixerKind::StateSpace) {
 		const yalm::SsmSpec &q = ls.ssm;
@@ -616,6 +660,11 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 		if (fuse && gemv_fusable(c, n, inner, L.wout, S.att)) return yalm_gemv_residual_sum(S.x, S.y1, S.att, L.wout, 1.f, inner, W, dt, nullptr, S.y, nsum, W, S.ticket, st);
 		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, inner, L.wout, n, W, inner, 1.f, st));
 	} else {
+		if (branch) {
+			sr = S.side[1];
+			ST_TRY(cudaEventRecord(S.fork[1], st));
+			ST_TRY(cudaStreamWaitEvent(sr, S.fork[1], 0));
+		}
 		// ---- left: sigmoid attention over the key ring and the kept first tokens ----
 		const yalm::MixerSpec &m = ls.mix;
 		const int nq = m.heads * m.dim, no = m.heads * m.vdim;
@@ -633,18 +682,19 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 		// ---- right: gated delta rule ----
 		const yalm::DeltaSpec &d = ls.delta;
 		const int dk = d.kv_heads * d.dim, dv = d.heads * d.vdim, dg = d.heads * d.dim, C = 2 * dk + dv, lda = dg + dv;
-		ST_TRY(yalm_conv_act_rows(S.conv, C, P + L.o_dq, ldp, L.conv_w, nullptr, L.conv_state, n, C, d.conv, pos0, ctl, st));
-		ST_TRY(stack_linear(*this, c, S.a16, S.aux, lda, P + L.o_a1, ldp, L.wa2, n, dg, d.decay_rank, 1.f, st));
-		ST_TRY(stack_linear(*this, c, S.a16, S.aux + dg, lda, P + L.o_g1, ldp, L.wg2, n, dv, d.gate_rank, 1.f, st));
+		ST_TRY(yalm_conv_act_rows(S.conv, C, P + L.o_dq, ldp, L.conv_w, nullptr, L.conv_state, n, C, d.conv, pos0, ctl, sr));
+		ST_TRY(stack_linear(*this, c, S.a16, S.aux, lda, P + L.o_a1, ldp, L.wa2, n, dg, d.decay_rank, 1.f, sr));
+		ST_TRY(stack_linear(*this, c, S.a16, S.aux + dg, lda, P + L.o_g1, ldp, L.wg2, n, dv, d.gate_rank, 1.f, sr));
 		ST_TRY(yalm_delta_prep_rows(S.conv, S.conv + dk, C, P + L.o_beta, ldp, S.aux, lda, L.d_a_log, L.d_dt_bias, n, d.heads, d.kv_heads, d.dim, 1e-6f,
-		                            1.0f / sqrtf((float)d.dim), st));
+		                            1.0f / sqrtf((float)d.dim), sr));
 		ST_TRY(yalm_state_scan_rows(S.scan, dv, S.conv + dk, C, S.conv, C, S.conv + 2 * dk, C, S.aux, lda, 1, nullptr, 0, P + L.o_beta, ldp, nullptr,
-		                            L.scan_state, n, d.heads, d.heads / d.kv_heads, d.dim, d.vdim, pos0, ctl, st));
-		ST_TRY(yalm_head_norm_gate_rows(S.att2, dv, S.scan, dv, S.aux + dg, lda, L.d_norm, n, d.heads, d.vdim, sp.norm_eps, st));
+		                            L.scan_state, n, d.heads, d.heads / d.kv_heads, d.dim, d.vdim, pos0, ctl, sr));
+		ST_TRY(yalm_head_norm_gate_rows(S.att2, dv, S.scan, dv, S.aux + dg, lda, L.d_norm, n, d.heads, d.vdim, sp.norm_eps, sr));
 		if (fuse && gemv_fusable(c, n, dv, L.wout, S.att2)) return yalm_gemv_residual_sum(S.x, S.y2, S.att2, L.wout, ls.right_scale, dv, W, dt, S.y1, S.y, nsum, W, S.ticket, st);
-		ST_TRY(stack_linear(*this, c, S.a16, S.y2, W, S.att2, dv, L.wout, n, W, dv, ls.right_scale, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.y2, W, S.att2, dv, L.wout, n, W, dv, ls.right_scale, sr));
 		mix_b = S.y2;
 	}
+	ST_TRY(join());
 	return yalm_residual_sum_rows(S.x, S.y1, mix_b, S.y, W, nsum, n, W, st);
 }
 
