@@ -211,7 +211,7 @@ struct Model::StackScratch {
 	char *arena = nullptr;
 	float *x = nullptr, *qkv = nullptr, *vfirst = nullptr, *att = nullptr, *y = nullptr, *gu = nullptr, *h = nullptr, *wts = nullptr, *xn = nullptr,
 	      *logits = nullptr, *probs = nullptr;
-	void *a16 = nullptr;
+	void *a16 = nullptr, *a16e = nullptr, *a16r = nullptr; // 16-bit operands of the tensor-core products: main stream, experts' stream, second mixer's stream
 	float *hs = nullptr, *conv = nullptr, *aux = nullptr, *scan = nullptr, *att2 = nullptr, *y1 = nullptr, *y2 = nullptr; // parallel blocks
 	float *attn_ws = nullptr; // split partials of decode-sized attention calls
 	int *ids = nullptr, *tokens = nullptr, *want = nullptr, *targets = nullptr;
@@ -477,7 +477,7 @@ void Model::cuda_stack(int device) {
 	             {(void **)&S.att, 4 * cap * std::max<size_t>(1, s.max_o_dim())},                   {(void **)&S.y, 4 * cap * top * W},
 	             {(void **)&S.gu, 4 * cap * 2 * ff},     {(void **)&S.h, 4 * cap * top * ff},    {(void **)&S.wts, 4 * cap * top},
 	             {(void **)&S.xn, 4 * cap * W},          {(void **)&S.logits, 4 * cap * (size_t)s.vocab}, {(void **)&S.probs, 4 * cap},
-	             {(void **)&S.a16, 2 * cap * top * kmax}, {(void **)&S.ids, 4 * cap * top},       {(void **)&S.tokens, 4 * cap},
+	             {(void **)&S.a16, 2 * cap * top * kmax}, {(void **)&S.a16e, pb * 2 * cap * top * kmax}, {(void **)&S.a16r, pb * 2 * cap * top * kmax}, {(void **)&S.ids, 4 * cap * top},       {(void **)&S.tokens, 4 * cap},
 	             {(void **)&S.want, 4 * cap},            {(void **)&S.targets, 4 * cap},
 	             {(void **)&S.attn_ws, 4 * yalm_attn_window_pool_workspace(256)}, {(void **)&S.ticket, 256},
 	             {(void **)&S.hs, pb * 4 * cap * W}, {(void **)&S.conv, pb * 4 * cap * nconv}, {(void **)&S.aux, pb * 4 * cap * naux},
@@ -554,7 +554,7 @@ static bool moe_grouped_off() { // YALM_STACK_MOE_TC=0: A/B against the slot ker
 	return off;
 }
 
-int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const float *x, int n, int act, cudaStream_t st) {
+int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const float *x, void *a16, int n, int act, cudaStream_t st) {
 	const Config &c = *config;
 	const FfnSpec &f = L.spec.ffn;
 	const int W = c.stack->width, ff = f.ff, top = f.top, E = f.experts, ns = n * top, bf16 = c.weight_dtype == DType::BF16;
@@ -571,22 +571,22 @@ int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const f
 		for (int s = 0; s < ns; ++s) order[at[ids[s]]++] = s; // stable: slots of an expert stay in row order
 	}
 	ST_TRY(cudaMemcpyAsync(S.order, order.data(), sizeof(int) * ns, cudaMemcpyHostToDevice, st));
-	ST_TRY(yalm_moe_gather_rows16(S.a16, x, W, S.order, S.wts, ns, top, W, bf16, f.weight_on_input ? 1 : 0, st));
+	ST_TRY(yalm_moe_gather_rows16(a16, x, W, S.order, S.wts, ns, top, W, bf16, f.weight_on_input ? 1 : 0, st));
 	const size_t es = dtype_size(c.weight_dtype);
 	for (int e = 0; e < E; ++e) {
 		const int m = start[e + 1] - start[e];
 		if (!m) continue;
-		const char *a = static_cast<const char *>(S.a16) + (size_t)start[e] * W * 2;
+		const char *a = static_cast<const char *>(a16) + (size_t)start[e] * W * 2;
 		float *gu = S.moe_gu + (size_t)start[e] * 2 * ff;
 		ST_TRY(yalm_gemm_16(gu, 2 * ff, a, static_cast<const char *>(L.wg) + (size_t)e * ff * W * es, m, ff, W, 0, bf16, 1.f, st));
 		ST_TRY(yalm_gemm_16(gu + ff, 2 * ff, a, static_cast<const char *>(L.wu) + (size_t)e * ff * W * es, m, ff, W, 0, bf16, 1.f, st));
 	}
 	ST_TRY(yalm_glu_act_rows(S.h, S.moe_gu, ns, ff, act, f.act_alpha, f.limit, f.up_offset, st));
-	ST_TRY(yalm_cast_rows16(S.a16, S.h, ff, ns, ff, bf16, st));
+	ST_TRY(yalm_cast_rows16(a16, S.h, ff, ns, ff, bf16, st));
 	for (int e = 0; e < E; ++e) {
 		const int m = start[e + 1] - start[e];
 		if (!m) continue;
-		ST_TRY(yalm_gemm_16(S.moe_ys + (size_t)start[e] * W, W, static_cast<const char *>(S.a16) + (size_t)start[e] * ff * 2,
+		ST_TRY(yalm_gemm_16(S.moe_ys + (size_t)start[e] * W, W, static_cast<const char *>(a16) + (size_t)start[e] * ff * 2,
 		                    static_cast<const char *>(L.wdown) + (size_t)e * W * ff * es, m, W, ff, 0, bf16, 1.f, st));
 	}
 	ST_TRY(yalm_moe_scatter_rows(S.y, W, S.moe_ys, W, S.order, S.wts, ns, W, f.weight_on_input ? 0 : 1, st));
@@ -605,38 +605,38 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 	const int ldp = ls.proj_width();
 	float *P = S.qkv;
 	const bool fuse = n == 1 && block_fuse_on();
+	const bool branch = !fuse && !branches_off(); // independent sublayers on side streams, see below
+	cudaStream_t se = st, sr = st;                // the experts' and the delta rule's streams
+	const FfnSpec &f = ls.ffn;
+	const int nsum = f.kind == FfnSpec::Moe ? f.top : 0;
 	if (fuse && sp.token_shift && gemv_fusable(c, n, W, L.wproj, S.x)) // a decode row: norm, shift and projection as one launch
 		ST_TRY(yalm_gemv_norm_shift(P, S.x, L.wproj, W, ldp, dt, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, S.xn, pos0, ctl, S.ticket, st));
 	else {
 		ST_TRY(yalm_norm_shift_rows(S.xn, sp.token_shift ? S.hs : nullptr, S.x, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, n, W, pos0, ctl, st));
-		ST_TRY(stack_linear(*this, c, S.a16, P, ldp, sp.token_shift ? S.hs : S.xn, W, L.wproj, n, ldp, W, 1.f, st));
-	}
-	// A decode row is a chain of small launches, each waiting for the one before.  The experts (which read h), the attention and
-	// the delta rule (which read disjoint columns of the projection and own their scratch) are independent: they run on side
-	// streams forked here and joined before the residual add.  One-row products do not touch the shared 16-bit operand buffer.
-	const bool branch = n == 1 && !fuse && !branches_off();
-	cudaStream_t se = st, sr = st; // the experts' and the delta rule's streams
-	// ---- experts on h (before the mixer, whose last product can carry the block's residual add on decode rows) ----
-	const FfnSpec &f = ls.ffn;
-	int nsum = 0;
-	if (f.kind == FfnSpec::Moe) {
-		if (branch) {
+		if (branch && nsum) { // h is complete: the experts wait for nothing that is enqueued after this point
 			se = S.side[0];
 			ST_TRY(cudaEventRecord(S.fork[0], st));
 			ST_TRY(cudaStreamWaitEvent(se, S.fork[0], 0));
 		}
+		ST_TRY(stack_linear(*this, c, S.a16, P, ldp, sp.token_shift ? S.hs : S.xn, W, L.wproj, n, ldp, W, 1.f, st));
+	}
+	// The experts (which read h), the attention and the delta rule (which read disjoint columns of the projection and own their
+	// scratch and 16-bit operand buffers) are independent: they run on side streams forked here and joined before the residual
+	// add.  A decode row is a chain of small launches, a prompt portion's products leave most SMs idle (16 to 64 CTAs each): both
+	// overlap.  Inside a captured decode step the streams become parallel branches of the graph.
+	// ---- experts on h ----
+	auto experts = [&]() -> int {
+		if (!nsum) return 0;
 		const int act = f.act == yalm::GluAct::SigmoidScaled ? 2 : f.act == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
 		ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.xn, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
 		                             f.renormalize ? 1 : 0, f.renorm_eps, f.groups, f.keep_groups, se));
 		if (S.moe_gu && !ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
-			ST_TRY(stack_moe_grouped(S, L, S.xn, n, act, se));
-		else {
-			ST_TRY(yalm_moe_glu_slots(S.h, S.xn, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
-			                          f.weight_on_input ? 1 : 0, se));
-			ST_TRY(yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, se));
-		}
-		nsum = f.top;
-	}
+			return stack_moe_grouped(S, L, S.xn, se == st ? S.a16 : S.a16e, n, act, se); // waits on the host for the chosen experts
+		ST_TRY(yalm_moe_glu_slots(S.h, S.xn, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
+		                          f.weight_on_input ? 1 : 0, se));
+		return yalm_moe_down_slots(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, se);
+	};
+	if (!branch) ST_TRY(experts()); // one stream: before the mixer, whose last product can then carry the block's residual add
 	auto join = [&]() -> int { // the side streams' work precedes what follows on the caller's stream
 		if (se != st) {
 			ST_TRY(cudaEventRecord(S.join[0], se));
@@ -683,17 +683,18 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 		const yalm::DeltaSpec &d = ls.delta;
 		const int dk = d.kv_heads * d.dim, dv = d.heads * d.vdim, dg = d.heads * d.dim, C = 2 * dk + dv, lda = dg + dv;
 		ST_TRY(yalm_conv_act_rows(S.conv, C, P + L.o_dq, ldp, L.conv_w, nullptr, L.conv_state, n, C, d.conv, pos0, ctl, sr));
-		ST_TRY(stack_linear(*this, c, S.a16, S.aux, lda, P + L.o_a1, ldp, L.wa2, n, dg, d.decay_rank, 1.f, sr));
-		ST_TRY(stack_linear(*this, c, S.a16, S.aux + dg, lda, P + L.o_g1, ldp, L.wg2, n, dv, d.gate_rank, 1.f, sr));
+		ST_TRY(stack_linear(*this, c, sr == st ? S.a16 : S.a16r, S.aux, lda, P + L.o_a1, ldp, L.wa2, n, dg, d.decay_rank, 1.f, sr));
+		ST_TRY(stack_linear(*this, c, sr == st ? S.a16 : S.a16r, S.aux + dg, lda, P + L.o_g1, ldp, L.wg2, n, dv, d.gate_rank, 1.f, sr));
 		ST_TRY(yalm_delta_prep_rows(S.conv, S.conv + dk, C, P + L.o_beta, ldp, S.aux, lda, L.d_a_log, L.d_dt_bias, n, d.heads, d.kv_heads, d.dim, 1e-6f,
 		                            1.0f / sqrtf((float)d.dim), sr));
 		ST_TRY(yalm_state_scan_rows(S.scan, dv, S.conv + dk, C, S.conv, C, S.conv + 2 * dk, C, S.aux, lda, 1, nullptr, 0, P + L.o_beta, ldp, nullptr,
 		                            L.scan_state, n, d.heads, d.heads / d.kv_heads, d.dim, d.vdim, pos0, ctl, sr));
 		ST_TRY(yalm_head_norm_gate_rows(S.att2, dv, S.scan, dv, S.aux + dg, lda, L.d_norm, n, d.heads, d.vdim, sp.norm_eps, sr));
 		if (fuse && gemv_fusable(c, n, dv, L.wout, S.att2)) return yalm_gemv_residual_sum(S.x, S.y2, S.att2, L.wout, ls.right_scale, dv, W, dt, S.y1, S.y, nsum, W, S.ticket, st);
-		ST_TRY(stack_linear(*this, c, S.a16, S.y2, W, S.att2, dv, L.wout, n, W, dv, ls.right_scale, sr));
+		ST_TRY(stack_linear(*this, c, sr == st ? S.a16 : S.a16r, S.y2, W, S.att2, dv, L.wout, n, W, dv, ls.right_scale, sr));
 		mix_b = S.y2;
 	}
+	if (branch) ST_TRY(experts()); // enqueued last: its host wait (prompt portions) then overlaps the mixer's kernels
 	ST_TRY(join());
 	return yalm_residual_sum_rows(S.x, S.y1, mix_b, S.y, W, nsum, n, W, st);
 }
@@ -767,7 +768,7 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 			ST_TRY(yalm_router_topk_rows(S.ids, S.wts, S.x, W, L.router, dt, n, f.experts, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
 			                             f.renormalize ? 1 : 0, f.renorm_eps, f.groups, f.keep_groups, st));
 			if (S.moe_gu && !from_ctl && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
-				ST_TRY(stack_moe_grouped(S, L, S.x, n, act, st));
+				ST_TRY(stack_moe_grouped(S, L, S.x, S.a16, n, act, st));
 			else {
 				ST_TRY(yalm_moe_glu_slots(S.h, S.x, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
 				                          f.weight_on_input ? 1 : 0, st));
