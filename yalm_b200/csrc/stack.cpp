@@ -609,17 +609,25 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 	cudaStream_t se = st, sr = st;                // the experts' and the delta rule's streams
 	const FfnSpec &f = ls.ffn;
 	const int nsum = f.kind == FfnSpec::Moe ? f.top : 0;
-	if (fuse && sp.token_shift && gemv_fusable(c, n, W, L.wproj, S.x)) // a decode row: norm, shift and projection as one launch
-		ST_TRY(yalm_gemv_norm_shift(P, S.x, L.wproj, W, ldp, dt, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, S.xn, pos0, ctl, S.ticket, st));
-	else {
-		ST_TRY(yalm_norm_shift_rows(S.xn, sp.token_shift ? S.hs : nullptr, S.x, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, n, W, pos0, ctl, st));
-		if (branch && nsum) { // h is complete: the experts wait for nothing that is enqueued after this point
+	// The experts only need h.  A prompt portion forks them before the projection (its product leaves SMs idle at small widths:
+	// +7 % at width 1024); a decode row forks them after it: the projection streams its weights at the memory's rate, the mixer's
+	// small kernels after it do not, and that is where the experts' traffic fits (forking earlier measured 5 % slower per row).
+	auto fork_experts = [&]() -> int {
+		if (branch && nsum) {
 			se = S.side[0];
 			ST_TRY(cudaEventRecord(S.fork[0], st));
 			ST_TRY(cudaStreamWaitEvent(se, S.fork[0], 0));
 		}
+		return 0;
+	};
+	if (fuse && sp.token_shift && gemv_fusable(c, n, W, L.wproj, S.x)) // a decode row: norm, shift and projection as one launch
+		ST_TRY(yalm_gemv_norm_shift(P, S.x, L.wproj, W, ldp, dt, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, S.xn, pos0, ctl, S.ticket, st));
+	else {
+		ST_TRY(yalm_norm_shift_rows(S.xn, sp.token_shift ? S.hs : nullptr, S.x, L.norm1, sp.norm_scalar, woff, sp.norm_eps, L.shift, L.hprev, n, W, pos0, ctl, st));
+		if (n > 1) ST_TRY(fork_experts());
 		ST_TRY(stack_linear(*this, c, S.a16, P, ldp, sp.token_shift ? S.hs : S.xn, W, L.wproj, n, ldp, W, 1.f, st));
 	}
+	if (n == 1) ST_TRY(fork_experts());
 	// The experts (which read h), the attention and the delta rule (which read disjoint columns of the projection and own their
 	// scratch and 16-bit operand buffers) are independent: they run on side streams forked here and joined before the residual
 	// add.  A decode row is a chain of small launches, a prompt portion's products leave most SMs idle (16 to 64 CTAs each): both
