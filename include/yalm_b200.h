@@ -269,8 +269,8 @@ int yalm_norm_shift_rows(float *h, float *hs, const float *x, const float *w, in
  * (channels, taps - 1): the inputs of the positions just before the call, replaced by the call's last ones. */
 int yalm_conv_act_rows(float *out, int ldo, const float *in, int ldi, const float *w, const float *bias, float *state, int n, int channels,
                        int taps, int pos0, const int *ctl, yalm_stream_t s);
-/* Linear recurrence over a (D, P) matrix state per head: S <- decay S; u = beta (v - S^T k) if beta, else vscale v;
- * S <- S + k u^T; out = S^T q (+ skip v).  k, q (n, kv heads D), head h reading kv head h / rep; v, out (n, heads P);
+/* Linear recurrence over a (D, P) matrix state M per head: M <- a M (a: the decay); e = beta (v - M^T k) if beta, else vscale v;
+ * M <- M + k e^T; out = M^T q (+ skip v).  k, q (n, kv heads D), head h reading kv head h / rep; v, out (n, heads P);
  * decay (n, heads) or, if decay_per_channel, (n, heads D) acting on rows; vscale, beta (n, heads) or null; skip (heads) or
  * null; state (heads, P, D).  D <= 256. */
 int yalm_state_scan_rows(float *out, int ldo, const float *k, int ldk, const float *q, int ldq, const float *v, int ldv, const float *decay,

@@ -50,7 +50,7 @@ def causal_conv(x, w, b=None):
 # ---- the state-space mixer ----------------------------------------------------------------------------------------------
 def mamba2_mixer(h, W, p, m, eps):
     """m: heads, vdim, state, groups, norm_groups, conv.  Per head a (state, vdim) matrix S:
-    S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x."""
+    a = exp(-exp(A_log) dt);  M <- a M + dt B x^T;  y = M^T C + D x."""
     H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
     inner, T = H * P, h.shape[0]
     u = h @ W[p + "in"].T
@@ -114,8 +114,8 @@ def sigmoid_attention(h, W, p, m):
 
 
 def matrix_state_scan(k, q, v, decay, beta=None, vscale=None, skip=None):
-    """k, q (T, H, D), v (T, H, P), decay (T, H) or (T, H, D): S <- decay S; u = beta (v - S^T k) or vscale v;
-    S <- S + k u^T; o = S^T q + skip v.  Returns (o, final S)."""
+    """k, q (T, H, D), v (T, H, P), decay a (T, H) or (T, H, D): M <- a M; e = beta (v - M^T k) or vscale v;
+    M <- M + k e^T; y = M^T q + skip v.  Returns (y, final M)."""
     T, H, D = k.shape
     P = v.shape[2]
     S = np.zeros((H, D, P))
@@ -136,7 +136,7 @@ def matrix_state_scan(k, q, v, decay, beta=None, vscale=None, skip=None):
 
 def gated_delta_mixer(h, W, p, m, eps):
     """Per head a (dim, vdim) matrix S with one decay per key channel:
-    S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q."""
+    M <- diag(a) M;  e = beta (v - M^T k);  M <- M + k e^T;  y = M^T q."""
     H, G, d, P, T = m["heads"], m["kv_heads"], m["dim"], m["vdim"], h.shape[0]
     q = silu(causal_conv(h @ W[p + "q"].T, W[p + "q.conv"])).reshape(T, G, d)
     k = silu(causal_conv(h @ W[p + "k"].T, W[p + "k.conv"])).reshape(T, G, d)

@@ -48,7 +48,7 @@ struct MixerSpec {
 };
 
 // Selective state-space mixer (state-space duality form): per head a (state, vdim) matrix S,
-// S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, after one projection [z | x | B | C | dt] and a short causal
+// M <- a M + (dt x) B^T-wise outer product, i.e. M += dt B x^T after the decay a = exp(-exp(A_log) dt); read-out y = M^T C + D x; after one projection [z | x | B | C | dt] and a short causal
 // convolution + SiLU over x, B, C; y * silu(z) is RMS-normed in norm_groups parts.
 struct SsmSpec {
 	int heads = 0, vdim = 0, state = 0, groups = 0, norm_groups = 1, conv = 0;
@@ -58,7 +58,7 @@ struct SsmSpec {
 };
 
 // Gated delta rule with one decay per head and key channel: per head a (dim, vdim) matrix S,
-// S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  q, k (kv_heads x dim) and v (heads x vdim) pass a
+// decay the rows, M <- diag(a) M; correct what M holds for this key, e = beta (v - M^T k), M <- M + k e^T; read out y = M^T q.  q, k (kv_heads x dim) and v (heads x vdim) pass a
 // short causal convolution + SiLU; q, k are unit vectors per head; the decay and the output gate come from two-stage
 // (low-rank) projections whose inner sizes are the checkpoint's.
 struct DeltaSpec {

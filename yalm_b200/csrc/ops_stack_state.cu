@@ -9,7 +9,7 @@
 //   norm_shift_rows        h = rms(x) * w (one weight per channel or one number) and, optionally, the token-shifted copy
 //                          hs = h + (h of the previous position - h) * mu
 //   conv_act_rows          per-channel causal convolution over the last `taps` positions (+ bias) and SiLU
-//   state_scan_rows        S <- decay * S;  u = beta (v - S^T k)  or  u = vscale * v;  S <- S + k u^T;  o = S^T q (+ skip * v)
+//   state_scan_rows        M <- a * M;  e = beta (v - M^T k)  or  e = vscale * v;  M <- M + k e^T;  y = M^T q (+ skip * v)
 //                          with a scalar or per-key-channel decay: both the state-space recurrence and the gated delta rule
 //   ssm_prep_rows          dt = softplus(raw + bias), decay = exp(-exp(A_log) dt)
 //   delta_prep_rows        unit q / k per head, beta = sigmoid(raw), per-channel decay from raw step sizes
@@ -102,16 +102,16 @@ __global__ void __launch_bounds__(128) conv_state_rows_kernel(const float *__res
 }
 
 // ---- linear recurrence over a matrix state -----------------------------------------------------------------------------------
-// Per head a (D, P) matrix S whose columns evolve independently:
-//   S <- decay * S   (decay: one number per head, or one per head and key channel, acting on rows)
-//   u = beta * (v - S^T k)   (delta rule)   or   u = vscale * v
-//   S <- S + k u^T;   o = S^T q  (+ skip * v)
+// Per head a (D, P) matrix M whose columns evolve independently:
+//   M <- a * M       (the decay a: one number per head, or one per head and key channel, acting on rows)
+//   e = beta * (v - M^T k)   (delta rule)   or   e = vscale * v
+//   M <- M + k e^T;   y = M^T q  (+ skip * v)
 // One CTA owns 16 columns of one head; 8 neighbouring lanes share a column, lane `sub` holding the EPL consecutive rows
 // sub * EPL .. in registers, so the two dot products of a step are EPL multiply-adds (four partial sums) and three shuffles.
 // k, q, the decays and v of 8 positions at a time go global -> shared with cp.async into one of two stages: the next 8 load
 // while these are consumed.  In shared memory a position's row is cut into the 8 lanes' segments, padded so that the lanes'
 // 16-byte reads fall into different banks.  The reduction of a position's output is carried into the next position's step,
-// where it shares the shuffle rounds of that step's S^T k, so only the recurrence itself (decay, S^T k, update) is a serial
+// where it shares the shuffle rounds of that step's M^T k, so only the recurrence itself (decay, M^T k, update) is a serial
 // chain.  The order of every sum is fixed, so a position's output does not depend on how the rows were cut into calls.
 // State in global memory: (head, column, row) fp32.
 struct ScanArgs {
