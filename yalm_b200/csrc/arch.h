@@ -47,9 +47,9 @@ struct MixerSpec {
 	int rel_far = 0;             // rel_rows / 2 have a row each, the rest are spaced logarithmically up to rel_far, then the last row
 };
 
-// Selective state-space mixer (state-space duality form): per head a (state, vdim) matrix S,
-// M <- a M + (dt x) B^T-wise outer product, i.e. M += dt B x^T after the decay a = exp(-exp(A_log) dt); read-out y = M^T C + D x; after one projection [z | x | B | C | dt] and a short causal
-// convolution + SiLU over x, B, C; y * silu(z) is RMS-normed in norm_groups parts.
+// Selective state-space mixer (state-space duality form): one projection [z | x | B | C | dt], a short causal convolution +
+// SiLU over x, B, C; per head a (state, vdim) matrix M with a scalar decay a = exp(-exp(A_log) dt): M <- a M + dt B x^T,
+// read-out y = M^T C + D x; y * silu(z) is RMS-normed in norm_groups parts.
 struct SsmSpec {
 	int heads = 0, vdim = 0, state = 0, groups = 0, norm_groups = 1, conv = 0;
 	int inner() const { return heads * vdim; }
